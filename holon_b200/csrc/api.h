@@ -151,14 +151,14 @@ int hb_latent_attention_bf16(void* out, float* scratch, const void* qa, const vo
 // row, token_of[row] = its token. hb_expert_linear: out [rows, n] = act(x[token_of ? token_of[row] : row] · w[e]ᵀ) for
 // the rows of expert e, w [experts, n, k]; act 0 none, 1 relu squared, 2 silu. hb_expert_combine: out [tokens, hidden] =
 // sum_k weight[t, k] · y[place[t, k]] + (shared ? sigmoid(z[t, gate_at]) · shared[t] : 0).
-int hb_route_top(int32_t* chosen, float* weight, int32_t* counts, const float* z, int ld, int tokens, int experts,
+int hb_route_top(int32_t* chosen, float* weight, int32_t* counts, const float* z, const float* bias, int ld, int tokens, int experts,
                  int top, float scale, int renormalize, hb_stream stream);
 int hb_expert_rows(int32_t* place, int32_t* token_of, int32_t* counts, const int32_t* chosen, int tokens, int top,
                    int experts, hb_stream stream);
 // hb_route_top and hb_expert_rows as one call (one launch for up to 256 tokens and 1,024 experts). counts [2 experts + 3]
 // need not be zeroed; afterwards counts[2 experts + 1 ..] = (0, tokens): the `starts` of one expert that takes every token.
-int hb_route_rows(int32_t* chosen, float* weight, int32_t* counts, int32_t* place, int32_t* token_of, const float* z, int ld,
-                  int tokens, int experts, int top, float scale, int renormalize, hb_stream stream);
+int hb_route_rows(int32_t* chosen, float* weight, int32_t* counts, int32_t* place, int32_t* token_of, const float* z,
+                  const float* bias, int ld, int tokens, int experts, int top, float scale, int renormalize, hb_stream stream);
 int hb_expert_linear(void* out, const void* x, int dtype, const int32_t* token_of, const void* w, const int32_t* starts,
                      int rows, int experts, int n, int k, int act, hb_stream stream);
 int hb_expert_combine(void* out, const void* y, int dtype, const int32_t* place, const float* weight, const void* shared,
@@ -325,11 +325,11 @@ int hb_glu_clamped(void* out, const void* gate_up, const void* bias, int dtype, 
 // query_start[b] .. query_start[b + 1] and lives in slot row_slot[b].
 // The scan. qk [tokens, 2, kv_heads, dim] (queries, then keys), v [tokens, heads, vdim], state [slots, heads, vdim, dim]
 // (S column by column), all 32-bit; head h reads key head h / (heads / kv_heads). Per token: S <- g S with g = decay[t, h, :] (per key channel)
-// or head_decay[h] (give exactly one of the two); u = beta[t, h] (v - S^T k) (beta null: u = v); S <- S + k u^T;
+// or head_decay[h] or token_decay[t, h] (give exactly one of the three; no beta with the last); u = beta[t, h] (v - S^T k) (beta null: u = v); S <- S + k u^T;
 // out[t, h, :] = S^T q. The state is read at the start of a row and written back at its end. `most`: no row brings more
 // tokens than this (0: unknown); it bounds the stage of tokens a block keeps in shared memory.
 int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
-                      const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
+                      const float* token_decay, const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
                       int heads, int kv_heads, int dim, int vdim, int most, hb_stream stream);
 // A delta-rule mixer's first product, rows [q | k | v | b] of `dtype`, `ld` apart, and the outputs of its two low-rank
 // projections, low2 [tokens, heads dim + heads vdim] in 32-bit, become the scan's inputs: q, k, v through a causal
@@ -352,6 +352,46 @@ int hb_retention_prepare(float* qk, float* v, const void* first, int dtype, int 
 // 32-bit multiplier gate_mul [tokens, heads vdim], or silu of gate_pre (rows `ld` apart, `dtype`), or none.
 int hb_head_norm_gate(void* out, const float* o, int dtype, const float* weight, const float* gate_mul,
                       const void* gate_pre, long ld, float eps, int tokens, int heads, int vdim, hb_stream stream);
+
+// ---- the matrix memory with exponential gates (csrc/mlstm.cu): the kernels around hb_recurrent_scan with token_decay.
+// pre [tokens, ld] 32-bit: the input gate's pre-activations of the heads, then the forget gate's; bias [2 heads] likewise.
+// out [3][tokens, heads]: keep = exp(f + m' - m), take = exp(i - m), exp(-m), with i = cap tanh(. / cap),
+// f = logsigmoid(cap tanh(. / cap)), m = max(f + m', i); m_state [slots, heads] carries m from step to step.
+int hb_mlstm_gates(float* out, const float* pre, int ld, const void* bias, int bias_dtype, float cap, float* m_state,
+                   const int32_t* query_start, const int32_t* row_slot, int rows, int tokens, int heads, hb_stream stream);
+// first rows [q (heads dim) | k (heads dim) | v (heads vdim) | ...] -> qk [tokens, 2, heads, dim] = (q q_scale, k take[t, h]),
+// v1 [tokens, heads, vdim + 1] = [v | 1].
+int hb_mlstm_prepare(float* qk, float* v1, const float* take, const void* first, int dtype, int ld, int tokens, int heads,
+                     int dim, int vdim, float q_scale, hb_stream stream);
+// o1 [tokens, heads, vdim + 1] = the scan's rows: y = o1[:vdim] / (max(|o1[vdim]|, floor[t, h]) + tiny), each head's y
+// divided by its root mean square (eps), times weight [heads vdim], times sigmoid(gate_pre) (rows `ld` apart).
+int hb_mlstm_read_out(void* out, const float* o1, const float* floor_, int dtype, const void* weight, int weight_dtype,
+                      const void* gate_pre, long ld, float eps, float tiny, int tokens, int heads, int vdim, hb_stream stream);
+
+// ---- a norm on a sublayer's output, with the average over the layers' results (csrc/elementwise.cu)
+// dst = src + N(y + bias), N(z) = z rsqrt(mean(z^2) + eps) (weight + offset); y null: dst = src. With hist (n_hist tensors
+// [rows, dim], hist_stride elements apart, dst the last of them): avg = sum_j coef[j] hist[j]. cast (or null) gets what goes
+// on (avg with hist, else dst) as `cast_dtype`.
+int hb_out_norm_add(float* dst, const float* src, const void* y, int y_dtype, const void* bias, int bias_dtype,
+                    const void* weight, int weight_dtype, float eps, float offset, const float* hist, long hist_stride,
+                    int n_hist, const float* coef, float* avg, void* cast, int cast_dtype, int rows, int dim, hb_stream stream);
+
+// ---- attention whose heads share their weights after the softmax, keys and values of unequal sizes (csrc/attention_talking.cu)
+// cache [pages, kv_heads, page_size, key_dim + value_dim]. qkv rows [q | k | v] -> bias, RMSNorm of q and k per head with
+// q_weight / k_weight [key_dim] (null: none), the first rot_dims channels turned (neighbouring pairs if `interleaved`, else
+// half-split; table [table_rows, rot_dims] cosines then sines), values blended with `first` [tokens, kv_heads, value_dim] by
+// blend[0]; `keep` receives the unblended values in 32-bit.
+int hb_qkv_talking_prepare(void* q_out, void* kv, float* keep, const void* qkv, int dtype, const void* bias, int bias_dtype,
+                           const void* q_weight, const void* k_weight, int weight_dtype, float eps, const int32_t* positions,
+                           const float* table, int rot_dims, int table_rows, int interleaved, const float* first,
+                           const float* blend, const int32_t* write_index, int pages, int page_size, int tokens, int heads,
+                           int kv_heads, int key_dim, int value_dim, hb_stream stream);
+// out [tokens, heads, value_dim]: softmax of q . k scale head_scale[h] over the keys a query sees (j <= i; chunk C > 0: of its
+// own block of C positions; window W > 0: the last W), the heads' weights mixed by talk [heads, heads] (null: not mixed).
+int hb_attention_talking(void* out, const void* q, const void* kv, int dtype, const int32_t* block_table, int table_stride,
+                         const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int rows, int tokens,
+                         int heads, int kv_heads, int key_dim, int value_dim, int pages, int page_size, float scale,
+                         const float* head_scale, int chunk, int window, const float* talk, hb_stream stream);
 
 #ifdef __cplusplus
 }

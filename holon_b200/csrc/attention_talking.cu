@@ -1,0 +1,284 @@
+// Attention whose heads share their softmax weights after the softmax ("talking heads"), over a paged cache that keeps a
+// token's key and value of one kv head side by side in one row (key_dim + value_dim numbers, the two sizes free of one
+// another): cache [pages, kv_heads, page_size, key_dim + value_dim].
+//
+//   p_g(i, j)   = softmax_j(q_g(i) . k_kv(g)(j) * scale * head_scale[g]) over the keys j that i may see
+//   out_h(i)    = sum_j (sum_g talk[h, g] p_g(i, j)) v_kv(h)(j)  =  sum_g talk[h, g] (sum_j p_g(i, j) v_kv(h)(j))
+//
+// so a query head's weights are applied to the values of EVERY kv head, normalised by that head's own denominator, and
+// the mixing matrix then takes what each output head needs: no weight ever leaves its kernel. Which keys a query at
+// position i sees: j <= i, with `chunk` C > 0 only those of its own block (j >= floor(i / C) C, blocks counted from the
+// sequence's first token), with `window` W > 0 only j > i - W. Scores, weights and sums are 32-bit whatever the storage.
+//
+// hb_qkv_talking_prepare  a first product's rows [q | k | v] -> bias, per-head RMSNorm of q and k, rotation, the value
+//                         blend with an earlier layer's values, q rows and the cache's [k | v] rows
+// hb_attention_talking    any sizes on CUDA cores, 32-bit arithmetic: the float32 engine's kernel, and the bfloat16
+//                         engine's for sizes the tensor-core kernel refuses
+#include "common.cuh"
+
+__device__ __forceinline__ float load_any(const void* p, int f32, size_t i) {
+    return f32 ? ((const float*)p)[i] : to_f32(((const bf16*)p)[i]);
+}
+
+// ---------------------------------------------------------------- from the first product to q rows and cache rows
+// One warp per (token, head slot): heads query slots, kv_heads key slots, kv_heads value slots. A q or k head: x + bias,
+// x / sqrt(mean(x^2) + eps) * weight (if a weight is given), the first rot_dims channels turned by the token's position:
+// in neighbouring pairs (2c, 2c + 1) if `interleaved`, else in half-split pairs (c, c + rot_dims / 2); `table` holds, per
+// position, the rot_dims / 2 cosines and then the sines. One rounding, at the end. A value head: x + bias; with `blend`,
+// (1 - blend[0]) x + blend[0] first[t, slot, :]; with `keep`, the 32-bit value is also left there for later layers.
+#define TP_WARPS 4
+#define TP_PER_LANE 16            // head sizes up to 512
+template <typename T>
+__global__ void talking_prepare_kernel(T* __restrict__ q_out, T* __restrict__ kv, float* __restrict__ keep,
+                                       const T* __restrict__ qkv, const void* __restrict__ bias, int bias_f32,
+                                       const void* __restrict__ q_weight, const void* __restrict__ k_weight, int weight_f32,
+                                       float eps, const int32_t* __restrict__ positions, const float* __restrict__ table,
+                                       int rot_dims, int table_rows, int interleaved, const float* __restrict__ first,
+                                       const float* __restrict__ blend, const int32_t* __restrict__ write_index,
+                                       int pages, int page_size, int tokens, int heads, int kv_heads, int kd, int vd) {
+    extern __shared__ float tp_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slots = heads + 2 * kv_heads;
+    const long item = (long)blockIdx.x * TP_WARPS + warp;
+    if (item >= (long)tokens * slots) return;
+    const int t = (int)(item / slots), slot = (int)(item % slots);
+    const int width = heads * kd + kv_heads * (kd + vd);
+    const T* row = qkv + (size_t)t * width;
+    const long w = write_index ? write_index[t] : -1;
+    const bool stored = w >= 0 && w < (long)pages * page_size;
+    const int rowlen = kd + vd;
+    if (slot >= heads + kv_heads) {                                   // a value head
+        const int c = slot - heads - kv_heads, at = heads * kd + kv_heads * kd + c * vd;
+        const float lam = blend ? blend[0] : 0.f;
+        T* dst = stored ? kv + (((size_t)(w / page_size) * kv_heads + c) * page_size + w % page_size) * rowlen + kd : nullptr;
+        for (int d = lane; d < vd; d += 32) {
+            float x = to_f32(row[at + d]) + (bias ? load_any(bias, bias_f32, at + d) : 0.f);
+            if (keep) keep[((size_t)t * kv_heads + c) * vd + d] = x;
+            if (blend) x = (1.f - lam) * x + lam * first[((size_t)t * kv_heads + c) * vd + d];
+            if (dst) dst[d] = from_f32<T>(x);
+        }
+        return;
+    }
+    const bool is_q = slot < heads;
+    const int head = is_q ? slot : slot - heads, at = is_q ? head * kd : heads * kd + head * kd;
+    const void* weight = is_q ? q_weight : k_weight;
+    float* ys = tp_smem + (size_t)warp * kd;
+    float x[TP_PER_LANE], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < TP_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        x[i] = d < kd ? to_f32(row[at + d]) + (bias ? load_any(bias, bias_f32, at + d) : 0.f) : 0.f;
+        ss += x[i] * x[i];
+    }
+    const float r = weight ? rsqrtf(warp_sum(ss) / (float)kd + eps) : 1.f;
+#pragma unroll
+    for (int i = 0; i < TP_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        if (d < kd) ys[d] = weight ? x[i] * r * load_any(weight, weight_f32, d) : x[i];
+    }
+    __syncwarp();
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= table_rows && table_rows > 0 ? table_rows - 1 : pos);
+    const float* cs = table ? table + (size_t)pos * rot_dims : nullptr;
+    const int half = rot_dims >> 1;
+    T* dst = is_q ? q_out + ((size_t)t * heads + head) * kd
+                  : (stored ? kv + (((size_t)(w / page_size) * kv_heads + head) * page_size + w % page_size) * rowlen : nullptr);
+    if (!dst) return;
+    for (int d = lane; d < kd; d += 32) {
+        float y = ys[d];
+        if (cs && d < rot_dims) {
+            int c, partner; bool lead;                                // lead: the pair's first member (u of (u, v))
+            if (interleaved) { c = d >> 1; partner = d ^ 1; lead = (d & 1) == 0; }
+            else { lead = d < half; c = lead ? d : d - half; partner = lead ? d + half : d - half; }
+            const float co = cs[c], si = cs[half + c], o = ys[partner];
+            y = lead ? y * co - o * si : y * co + o * si;
+        }
+        dst[d] = from_f32<T>(y);
+    }
+}
+
+extern "C" int hb_qkv_talking_prepare(void* q_out, void* kv, float* keep, const void* qkv, int dtype, const void* bias,
+                                      int bias_dtype, const void* q_weight, const void* k_weight, int weight_dtype, float eps,
+                                      const int32_t* positions, const float* table, int rot_dims, int table_rows,
+                                      int interleaved, const float* first, const float* blend, const int32_t* write_index,
+                                      int pages, int page_size, int tokens, int heads, int kv_heads, int key_dim,
+                                      int value_dim, hb_stream stream) {
+    if (tokens == 0) return 0;
+    if (key_dim < 1 || key_dim > 32 * TP_PER_LANE || value_dim < 1) HB_REFUSE("qkv_talking_prepare: key size %d (1 to %d), value size %d", key_dim, 32 * TP_PER_LANE, value_dim);
+    if (rot_dims < 0 || rot_dims % 2 || rot_dims > key_dim) HB_REFUSE("qkv_talking_prepare: %d rotated channels of %d", rot_dims, key_dim);
+    if (rot_dims && !table) HB_REFUSE("qkv_talking_prepare: a rotation needs its table");
+    if ((q_weight == nullptr) != (k_weight == nullptr)) HB_REFUSE("qkv_talking_prepare: give both norm weights or none");
+    if (blend && !first) HB_REFUSE("qkv_talking_prepare: a blend needs the first layer's values");
+    const long items = (long)tokens * (heads + 2 * kv_heads);
+    const unsigned blocks = (unsigned)((items + TP_WARPS - 1) / TP_WARPS);
+    const size_t smem = (size_t)TP_WARPS * key_dim * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (!rot_dims) table = nullptr;
+    if (dtype == HB_F32)
+        talking_prepare_kernel<float><<<blocks, TP_WARPS * 32, smem, s>>>(
+            (float*)q_out, (float*)kv, keep, (const float*)qkv, bias, bias_dtype == HB_F32, q_weight, k_weight,
+            weight_dtype == HB_F32, eps, positions, table, rot_dims, table_rows, interleaved, first, blend, write_index, pages,
+            page_size, tokens, heads, kv_heads, key_dim, value_dim);
+    else if (dtype == HB_BF16)
+        talking_prepare_kernel<bf16><<<blocks, TP_WARPS * 32, smem, s>>>(
+            (bf16*)q_out, (bf16*)kv, keep, (const bf16*)qkv, bias, bias_dtype == HB_F32, q_weight, k_weight,
+            weight_dtype == HB_F32, eps, positions, table, rot_dims, table_rows, interleaved, first, blend, write_index, pages,
+            page_size, tokens, heads, kv_heads, key_dim, value_dim);
+    else HB_REFUSE("qkv_talking_prepare: dtype %d", dtype);
+    HB_LAUNCH_CHECK("qkv_talking_prepare");
+    return 0;
+}
+
+// ---------------------------------------------------------------- the attention, any sizes, CUDA cores
+// One block per query token, a warp per query head (a warp takes several heads in turn where there are more than
+// TK_WARPS). A lane scores one key of a block of 32 (q in shared memory), the block's weights then sweep the value rows
+// of all kv heads: a lane owns every 32nd of the kv_heads * value_dim output numbers of its head (EPL of them). The
+// normalised results of all heads wait in shared memory, wide [heads][kv_heads * value_dim], and the block's threads then
+// mix them: out[h, d] = sum_g talk[h, g] wide[g][kv(h) value_dim + d] (talk null: the head's own result).
+#define TK_WARPS 16
+template <typename T, int EPL>
+__global__ void attention_talking_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ kv,
+                                         const int32_t* __restrict__ block_table, int table_stride,
+                                         const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
+                                         const int32_t* __restrict__ kv_len, int rows, int heads, int kv_heads, int kd,
+                                         int vd, int pages, int page_size, float scale,
+                                         const float* __restrict__ head_scale, int chunk, int window,
+                                         const float* __restrict__ talk) {
+    extern __shared__ float tk_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    const int all = kv_heads * vd, rowlen = kd + vd;
+    float* wide = tk_smem;                                   // [heads][all]
+    float* qs = wide + (size_t)heads * all + (size_t)warp * kd;
+
+    int lo = 0, hi = rows;                                   // the row b with query_start[b] <= t < query_start[b + 1]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (query_start[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int b = lo;
+    const int n = kv_len[b];
+    const int pos = n - query_start[b + 1] + t;              // the query's position in its sequence
+    const bool live = n > 0 && pos >= 0;
+    const int32_t* table = block_table + (size_t)row_slot[b] * table_stride;
+    int first = 0;
+    if (live && chunk > 0) first = (pos / chunk) * chunk;
+    if (live && window > 0) first = max(first, pos - window + 1);
+    const long head_shift = (long)page_size * rowlen;        // from a kv head's row to the next kv head's row of the token
+
+    long off[EPL];                                           // element e = lane + 32 i of [kv head][value]: where it lies
+#pragma unroll                                               // relative to the token's row of kv head 0
+    for (int i = 0; i < EPL; ++i) {
+        const int e = lane + 32 * i;
+        off[i] = e < all ? (long)(e / vd) * head_shift + kd + e % vd : -1;
+    }
+    for (int g = warp; g < heads; g += warps) {
+        float acc[EPL];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        if (live) {
+            const float sc = scale * (head_scale ? head_scale[g] : 1.f);
+            const T* qr = q + ((size_t)t * heads + g) * kd;
+            __syncwarp();
+            for (int d = lane; d < kd; d += 32) qs[d] = to_f32(qr[d]);
+            __syncwarp();
+            const int hk = g / (heads / kv_heads);
+            for (int j0 = first; j0 <= pos; j0 += 32) {
+                const int j = j0 + lane;
+                long base = -1;                              // element offset of key j's row of kv head 0
+                if (j <= pos) {
+                    const int page = table[j / page_size];
+                    if (page >= 0 && page < pages) base = (((long)page * kv_heads) * page_size + j % page_size) * rowlen;
+                }
+                float s = -INFINITY;
+                if (base >= 0) {
+                    const T* kr = kv + base + hk * head_shift;
+                    float dot = 0.f;
+                    for (int d = 0; d < kd; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
+                    s = dot * sc;
+                }
+                const float m_new = fmaxf(m, warp_max(s));
+                const float corr = m_new == -INFINITY ? 1.f : expf(m - m_new);
+                const float p = base >= 0 ? expf(s - m_new) : 0.f;
+                l = l * corr + warp_sum(p);
+                m = m_new;
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) acc[i] *= corr;
+                const int count = min(32, pos - j0 + 1);
+                for (int jj = 0; jj < count; ++jj) {
+                    const float pj = __shfl_sync(0xffffffffu, p, jj);
+                    const long bj = __shfl_sync(0xffffffffu, base, jj);
+                    if (bj < 0) continue;
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i)
+                        if (off[i] >= 0) acc[i] = fmaf(pj, to_f32(kv[bj + off[i]]), acc[i]);
+                }
+            }
+        }
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const int e = lane + 32 * i;
+            if (e < all) wide[(size_t)g * all + e] = acc[i] * inv;
+        }
+    }
+    __syncthreads();
+    const int group = heads / kv_heads;
+    for (int e = threadIdx.x; e < heads * vd; e += blockDim.x) {
+        const int h = e / vd, d = e - h * vd, at = (h / group) * vd + d;
+        float o;
+        if (talk) {
+            o = 0.f;
+            for (int g = 0; g < heads; ++g) o = fmaf(talk[h * heads + g], wide[(size_t)g * all + at], o);
+        } else {
+            o = wide[(size_t)h * all + at];
+        }
+        out[((size_t)t * heads + h) * vd + d] = from_f32<T>(o);
+    }
+}
+
+template <typename T>
+static int launch_talking(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
+                          const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int rows, int tokens,
+                          int heads, int kv_heads, int kd, int vd, int pages, int page_size, float scale,
+                          const float* head_scale, int chunk, int window, const float* talk, cudaStream_t s) {
+    const int all = kv_heads * vd;
+    const int warps = heads < TK_WARPS ? heads : TK_WARPS;
+    const size_t smem = ((size_t)heads * all + (size_t)warps * kd) * sizeof(float);
+    if (smem > 200 * 1024) HB_REFUSE("attention_talking: %d heads over %d kv heads of %d values need %zu bytes of shared memory", heads, kv_heads, vd, smem);
+#define HB_TALK(E) do { \
+        auto kernel = attention_talking_kernel<T, E>; \
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        kernel<<<tokens, warps * 32, smem, s>>>((T*)out, (const T*)q, (const T*)kv, block_table, table_stride, row_slot, \
+            query_start, kv_len, rows, heads, kv_heads, kd, vd, pages, page_size, scale, head_scale, chunk, window, talk); \
+    } while (0)
+    if (all <= 32) HB_TALK(1);
+    else if (all <= 64) HB_TALK(2);
+    else if (all <= 128) HB_TALK(4);
+    else if (all <= 256) HB_TALK(8);
+    else if (all <= 512) HB_TALK(16);
+    else if (all <= 1024) HB_TALK(32);
+    else HB_REFUSE("attention_talking: %d kv heads of %d values are above 1024 numbers a head", kv_heads, vd);
+#undef HB_TALK
+    HB_LAUNCH_CHECK("attention_talking");
+    return 0;
+}
+
+extern "C" int hb_attention_talking(void* out, const void* q, const void* kv, int dtype, const int32_t* block_table,
+                                    int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                                    const int32_t* kv_len, int rows, int tokens, int heads, int kv_heads, int key_dim,
+                                    int value_dim, int pages, int page_size, float scale, const float* head_scale, int chunk,
+                                    int window, const float* talk, hb_stream stream) {
+    if (tokens == 0 || rows == 0) return 0;
+    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_talking: %d heads are no multiple of %d kv heads", heads, kv_heads);
+    if (key_dim < 1 || value_dim < 1 || chunk < 0 || window < 0) HB_REFUSE("attention_talking: key size %d, value size %d, chunk %d, window %d", key_dim, value_dim, chunk, window);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == HB_F32)
+        return launch_talking<float>(out, q, kv, block_table, table_stride, row_slot, query_start, kv_len, rows, tokens, heads,
+                                     kv_heads, key_dim, value_dim, pages, page_size, scale, head_scale, chunk, window, talk, s);
+    if (dtype == HB_BF16)
+        return launch_talking<bf16>(out, q, kv, block_table, table_stride, row_slot, query_start, kv_len, rows, tokens, heads,
+                                    kv_heads, key_dim, value_dim, pages, page_size, scale, head_scale, chunk, window, talk, s);
+    HB_REFUSE("attention_talking: dtype %d", dtype);
+}

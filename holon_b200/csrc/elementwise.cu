@@ -525,3 +525,86 @@ extern "C" int hb_sum_norm(float* h, const void* x0, const void* x1, const void*
     HB_LAUNCH_CHECK("sum_norm");
     return 0;
 }
+
+// ---------------------------------------------------------------- a norm on a sublayer's OUTPUT, and the depth average
+// dst[r] = src[r] + N(y[r] + bias), N(z) = z * rsqrt(mean(z^2) + eps) * (weight + offset): the block "x <- x + norm(f(x))",
+// whose sublayers read the stream itself. y null: dst[r] = src[r] (nothing is normed). With `hist` (n_hist tensors
+// [rows, dim], hist_stride elements apart, of which dst is the last): avg[r] = sum_j coef[j] hist[j][r] in the order of j,
+// the average over everything earlier layers and the embedding have left. `cast` (or null) gets the rows that go on
+// (avg with hist, else dst) in the storage type `cast_dtype`: what the next sublayer's products read. 32-bit throughout.
+// One block per row; the row waits in shared memory between the two passes.
+template <typename T>
+__device__ __forceinline__ void out_norm_row(float* __restrict__ dst, const float* __restrict__ src, const T* __restrict__ y,
+                                             const void* __restrict__ bias, int bias_f32, const void* __restrict__ weight,
+                                             int weight_f32, float eps, float offset, const float* __restrict__ hist,
+                                             long hist_stride, int n_hist, const float* __restrict__ coef,
+                                             float* __restrict__ avg, void* __restrict__ cast, int cast_dtype, int dim,
+                                             float* row, float* scratch) {
+    const size_t r = blockIdx.x;
+    float ss = 0.f;
+    if (y) {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            float z = to_f32(y[r * dim + d]);
+            if (bias) z += bias_f32 ? ((const float*)bias)[d] : to_f32(((const bf16*)bias)[d]);
+            row[d] = z;
+            ss += z * z;
+        }
+        ss = block_sum(ss, scratch);
+    }
+    const float scale = rsqrtf(ss / (float)dim + eps);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float x = src[r * dim + d];
+        if (y) {
+            const float w = (weight_f32 ? ((const float*)weight)[d] : to_f32(((const bf16*)weight)[d])) + offset;
+            x += row[d] * scale * w;
+        }
+        if (y || dst != src) dst[r * dim + d] = x;
+        float go = x;
+        if (hist) {
+            go = 0.f;
+            for (int j = 0; j + 1 < n_hist; ++j) go = fmaf(coef[j], hist[(size_t)j * hist_stride + r * dim + d], go);
+            go = fmaf(coef[n_hist - 1], x, go);
+            avg[r * dim + d] = go;
+        }
+        if (cast) {
+            if (cast_dtype == HB_F32) ((float*)cast)[r * dim + d] = go;
+            else ((bf16*)cast)[r * dim + d] = __float2bfloat16_rn(go);
+        }
+    }
+}
+
+template <typename T>
+__global__ void out_norm_add_kernel(float* dst, const float* src, const T* y, const void* bias, int bias_f32,
+                                    const void* weight, int weight_f32, float eps, float offset, const float* hist,
+                                    long hist_stride, int n_hist, const float* coef, float* avg, void* cast, int cast_dtype,
+                                    int dim) {
+    extern __shared__ float on_row[];
+    __shared__ float scratch[33];
+    out_norm_row<T>(dst, src, y, bias, bias_f32, weight, weight_f32, eps, offset, hist, hist_stride, n_hist, coef, avg, cast,
+                    cast_dtype, dim, on_row, scratch);
+}
+
+extern "C" int hb_out_norm_add(float* dst, const float* src, const void* y, int y_dtype, const void* bias, int bias_dtype,
+                               const void* weight, int weight_dtype, float eps, float offset, const float* hist,
+                               long hist_stride, int n_hist, const float* coef, float* avg, void* cast, int cast_dtype,
+                               int rows, int dim, hb_stream stream) {
+    if (rows == 0) return 0;
+    if (dim < 1 || (size_t)dim * sizeof(float) > 200 * 1024) HB_REFUSE("out_norm_add: rows of %d numbers", dim);
+    if (y && !weight) HB_REFUSE("out_norm_add: a norm needs its weight");
+    if (hist && (n_hist < 1 || !coef || !avg)) HB_REFUSE("out_norm_add: the depth average needs its coefficients and a place for the result");
+    if (hist && dst != hist + (size_t)(n_hist - 1) * hist_stride) HB_REFUSE("out_norm_add: the layer's result is the last of the kept ones");
+    const size_t smem = (size_t)dim * sizeof(float);
+    const int threads = dim >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype == HB_F32 || !y) {
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(out_norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        out_norm_add_kernel<float><<<rows, threads, smem, s>>>(dst, src, (const float*)y, bias, bias_dtype == HB_F32, weight,
+            weight_dtype == HB_F32, eps, offset, hist, hist_stride, n_hist, coef, avg, cast, cast_dtype, dim);
+    } else if (y_dtype == HB_BF16) {
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(out_norm_add_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        out_norm_add_kernel<bf16><<<rows, threads, smem, s>>>(dst, src, (const bf16*)y, bias, bias_dtype == HB_F32, weight,
+            weight_dtype == HB_F32, eps, offset, hist, hist_stride, n_hist, coef, avg, cast, cast_dtype, dim);
+    } else HB_REFUSE("out_norm_add: dtype %d", y_dtype);
+    HB_LAUNCH_CHECK("out_norm_add");
+    return 0;
+}

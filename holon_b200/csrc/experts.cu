@@ -13,7 +13,8 @@
 // One block per token. softmax over all experts in 32-bit; the `top` largest scores, equal scores by ascending
 // expert; weight = score · scale, with `renormalize` divided by the chosen scores' sum first.
 __global__ void route_top_kernel(int32_t* __restrict__ chosen, float* __restrict__ weight, int32_t* __restrict__ counts,
-                                 const float* __restrict__ z, int ld, int experts, int top, float scale, int renormalize) {
+                                 const float* __restrict__ z, int ld, int experts, int top, float scale, int renormalize,
+                                 const float* __restrict__ bias) {
     extern __shared__ float sc[];                       // experts scores
     __shared__ float scratch[33];
     __shared__ float best_v[32];
@@ -21,10 +22,10 @@ __global__ void route_top_kernel(int32_t* __restrict__ chosen, float* __restrict
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const float* zr = z + (size_t)t * ld;
     float m = -INFINITY;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) m = fmaxf(m, zr[e]);
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) m = fmaxf(m, zr[e] + (bias ? bias[e] : 0.f));
     m = block_max(m, scratch);
     float sum = 0.f;
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) { const float p = expf(zr[e] - m); sc[e] = p; sum += p; }
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) { const float p = expf(zr[e] + (bias ? bias[e] : 0.f) - m); sc[e] = p; sum += p; }
     sum = block_sum(sum, scratch);
     const float inv = 1.f / sum;
     float taken = 0.f;
@@ -59,14 +60,14 @@ __global__ void route_top_kernel(int32_t* __restrict__ chosen, float* __restrict
     }
 }
 
-extern "C" int hb_route_top(int32_t* chosen, float* weight, int32_t* counts, const float* z, int ld, int tokens,
-                            int experts, int top, float scale, int renormalize, hb_stream stream) {
+extern "C" int hb_route_top(int32_t* chosen, float* weight, int32_t* counts, const float* z, const float* bias, int ld,
+                            int tokens, int experts, int top, float scale, int renormalize, hb_stream stream) {
     if (tokens == 0) return 0;
     if (experts < 1 || top < 1 || top > experts || ld < experts) HB_REFUSE("route_top: top %d of %d experts in rows of %d", top, experts, ld);
     if (experts > 8192) HB_REFUSE("route_top: %d experts are above 8192", experts);
     const int threads = experts > 256 ? 256 : experts > 64 ? 128 : 64;
     route_top_kernel<<<tokens, threads, (size_t)experts * sizeof(float), (cudaStream_t)stream>>>(
-        chosen, weight, counts, z, ld, experts, top, scale, renormalize);
+        chosen, weight, counts, z, ld, experts, top, scale, renormalize, bias);
     HB_LAUNCH_CHECK("route_top");
     return 0;
 }
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(256) route_rows_small_kernel(int32_t* __restri
                                                                int32_t* __restrict__ counts, int32_t* __restrict__ place,
                                                                int32_t* __restrict__ token_of, const float* __restrict__ z,
                                                                int ld, int tokens, int experts, int top, float scale,
-                                                               int renormalize) {
+                                                               int renormalize, const float* __restrict__ bias) {
     extern __shared__ float rs_smem[];
     float* sc = rs_smem;                                   // [8][experts]
     int* cnt = (int*)(sc + 8 * (size_t)experts);           // [experts]: counts, then cursors
@@ -150,10 +151,10 @@ __global__ void __launch_bounds__(256) route_rows_small_kernel(int32_t* __restri
     for (int t = warp; t < tokens; t += 8) {
         const float* zr = z + (size_t)t * ld;
         float m = -INFINITY;
-        for (int e = lane; e < experts; e += 32) m = fmaxf(m, zr[e]);
+        for (int e = lane; e < experts; e += 32) m = fmaxf(m, zr[e] + (bias ? bias[e] : 0.f));
         m = warp_max(m);
         float sum = 0.f;
-        for (int e = lane; e < experts; e += 32) { const float p = expf(zr[e] - m); my[e] = p; sum += p; }
+        for (int e = lane; e < experts; e += 32) { const float p = expf(zr[e] + (bias ? bias[e] : 0.f) - m); my[e] = p; sum += p; }
         sum = warp_sum(sum);
         __syncwarp();
         const float inv = 1.f / sum;
@@ -205,20 +206,20 @@ __global__ void expert_whole_kernel(int32_t* counts, int experts, int tokens) {
 // hb_route_top and hb_expert_rows as one call. counts [2 experts + 3] need not be zeroed; afterwards it also holds, at
 // 2 experts + 1, the pair (0, tokens).
 extern "C" int hb_route_rows(int32_t* chosen, float* weight, int32_t* counts, int32_t* place, int32_t* token_of,
-                             const float* z, int ld, int tokens, int experts, int top, float scale, int renormalize,
-                             hb_stream stream) {
+                             const float* z, const float* bias, int ld, int tokens, int experts, int top, float scale,
+                             int renormalize, hb_stream stream) {
     if (tokens == 0) return 0;
     if (experts < 1 || top < 1 || top > experts || ld < experts) HB_REFUSE("route_rows: top %d of %d experts in rows of %d", top, experts, ld);
     cudaStream_t s = (cudaStream_t)stream;
     if (tokens <= RS_TOKENS && experts <= RS_EXPERTS) {
         const size_t smem = ((size_t)8 * experts + 2 * experts + 1) * sizeof(float);
         if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(route_rows_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        route_rows_small_kernel<<<1, 256, smem, s>>>(chosen, weight, counts, place, token_of, z, ld, tokens, experts, top, scale, renormalize);
+        route_rows_small_kernel<<<1, 256, smem, s>>>(chosen, weight, counts, place, token_of, z, ld, tokens, experts, top, scale, renormalize, bias);
         HB_LAUNCH_CHECK("route_rows_small");
         return 0;
     }
     HB_CUDA(cudaMemsetAsync(counts, 0, (size_t)(2 * experts + 3) * sizeof(int32_t), s));
-    int rc = hb_route_top(chosen, weight, counts, z, ld, tokens, experts, top, scale, renormalize, stream);
+    int rc = hb_route_top(chosen, weight, counts, z, bias, ld, tokens, experts, top, scale, renormalize, stream);
     if (rc) return rc;
     rc = hb_expert_rows(place, token_of, counts, chosen, tokens, top, experts, stream);
     if (rc) return rc;
@@ -231,6 +232,7 @@ extern "C" int hb_route_rows(int32_t* chosen, float* weight, int32_t* counts, in
 __device__ __forceinline__ float expert_act(float v, int act) {
     if (act == 1) { v = fmaxf(v, 0.f); return v * v; }            // the square of relu
     if (act == 2) return v / (1.f + expf(-v));                   // silu
+    if (act == 3) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));   // gelu, tanh form
     return v;
 }
 

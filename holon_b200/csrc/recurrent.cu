@@ -1,7 +1,8 @@
 // Mixers whose memory is a matrix per head instead of a cache of keys: S [key channel, value channel] in 32-bit per
 // request slot and head (kept column by column: state [slots, heads, vdim, dim], so that the key channels a thread owns
 // lie side by side), updated token by token,
-//     S <- diag(g_t) S                      (g_t: a decay per key channel and token, or one fixed decay per head)
+//     S <- diag(g_t) S                      (g_t: a decay per key channel and token, one per head and token, or one fixed
+//                                            decay per head)
 //     u  = beta_t (v_t - S^T k_t)           (the delta rule; without beta: u = v_t)
 //     S <- S + k_t u^T,      o_t = S^T q_t  (the read-out sees the token's own write)
 // and the kernels around that scan: what turns a layer's first product into q, k, v, decays and gates (a short causal
@@ -39,7 +40,8 @@ __device__ __forceinline__ void cp_async_f32x4(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int DPT, int P, bool PER_CHANNEL, bool DELTA>
+// TOKEN: `head_decay` holds one decay per token and head [tokens, heads]; it rides in the stage's beta column (no delta rule then).
+template <int DPT, int P, bool PER_CHANNEL, bool DELTA, bool TOKEN = false>
 __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qk, const float* __restrict__ v,
                                       const float* __restrict__ decay, const float* __restrict__ head_decay,
                                       const float* __restrict__ beta, float* __restrict__ state,
@@ -60,10 +62,11 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
         const int d = ((i >> 2) * P + p) * 4 + (i & 3);
         S[i] = col && d < dim ? S_g[d] : 0.f;
     }
-    const float fixed = head_decay ? head_decay[h] : 1.f;
+    float fixed = head_decay && !TOKEN ? head_decay[h] : 1.f;
     const bool vec = (dim & 3) == 0;
     if (n == 1) {                            // a row of one token (a decode step): no stage, no barrier; every thread reads
         const size_t t = (size_t)t0;         // its own channels of k, q and the decays straight from global memory
+        if (TOKEN) fixed = head_decay[t * heads + h];
         auto four = [&](const float* base, int d, float fill) -> float4 {
             if (vec && d + 3 < dim) return *(const float4*)(base + d);
             return make_float4(d < dim ? base[d] : fill, d + 1 < dim ? base[d + 1] : fill, d + 2 < dim ? base[d + 2] : fill,
@@ -151,7 +154,8 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
             const int j = e / width, x = e - j * width;
             cp_async_f32(sv + j * VT + x, v + ((size_t)(t0 + j0 + j) * heads + h) * vdim + c0 + x);
         }
-        if (DELTA && (int)threadIdx.x < m) cp_async_f32(sb + threadIdx.x, beta + (size_t)(t0 + j0 + threadIdx.x) * heads + h);
+        if ((DELTA || TOKEN) && (int)threadIdx.x < m)
+            cp_async_f32(sb + threadIdx.x, (TOKEN ? head_decay : beta) + (size_t)(t0 + j0 + threadIdx.x) * heads + h);
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
 
@@ -189,6 +193,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                     S[4 * i] *= g.x; S[4 * i + 1] *= g.y; S[4 * i + 2] *= g.z; S[4 * i + 3] *= g.w;
                 }
             } else {
+                if (TOKEN) fixed = sb[j];
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) S[i] *= fixed;
             }
@@ -239,7 +244,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
 
 template <int DPT, int P>
 static int launch_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
-                       const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
+                       const float* token_decay, const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
                        int heads, int kv_heads, int dim, int vdim, int most, cudaStream_t s) {
     const int unit = 32 / P > 1 ? 32 / P : 1;                         // columns a warp holds
     int VT = vdim < 256 / P ? vdim : 256 / P;
@@ -255,6 +260,7 @@ static int launch_scan(float* out, const float* qk, const float* v, const float*
     const size_t smem = (size_t)2 * ((tb * per_token + 3) & ~3) * sizeof(float);
     auto kernel = decay ? (beta ? recurrent_scan_kernel<DPT, P, true, true> : recurrent_scan_kernel<DPT, P, true, false>)
                         : (beta ? recurrent_scan_kernel<DPT, P, false, true> : recurrent_scan_kernel<DPT, P, false, false>);
+    if (token_decay) { kernel = recurrent_scan_kernel<DPT, P, false, false, true>; head_decay = token_decay; }
     if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kernel<<<dim3(rows, heads, tiles), threads, smem, s>>>(out, qk, v, decay, head_decay, beta, state, query_start, row_slot,
                                                           heads, kv_heads, dim, vdim, VT, tb);
@@ -263,16 +269,17 @@ static int launch_scan(float* out, const float* qk, const float* v, const float*
 }
 
 extern "C" int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
-                                 const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot,
+                                 const float* token_decay, const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot,
                                  int rows, int heads, int kv_heads, int dim, int vdim, int most, hb_stream stream) {
     if (rows == 0) return 0;
     if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("recurrent_scan: %d heads are no multiple of %d key heads", heads, kv_heads);
     if (dim < 1 || dim > 1024 || vdim < 1) HB_REFUSE("recurrent_scan: key size %d (1 to 1024), value size %d", dim, vdim);
-    if ((decay != nullptr) == (head_decay != nullptr)) HB_REFUSE("recurrent_scan: give decays per channel and token, or one per head");
+    if ((decay != nullptr) + (head_decay != nullptr) + (token_decay != nullptr) != 1) HB_REFUSE("recurrent_scan: give decays per channel and token, per head and token, or one per head");
+    if (token_decay && beta) HB_REFUSE("recurrent_scan: the delta rule does not go with a decay per head and token");
     if (rows > 65535 * 32 || heads > 65535 || (vdim + 7) / 8 > 65535) HB_REFUSE("recurrent_scan: %d rows, %d heads, value size %d", rows, heads, vdim);
     if ((((uintptr_t)qk | (uintptr_t)decay) & 15) != 0) HB_REFUSE("recurrent_scan: qk and decay must lie on 16-byte boundaries");
     cudaStream_t s = (cudaStream_t)stream;
-#define HB_SCAN(D, PP) return launch_scan<D, PP>(out, qk, v, decay, head_decay, beta, state, query_start, row_slot, rows, heads, \
+#define HB_SCAN(D, PP) return launch_scan<D, PP>(out, qk, v, decay, head_decay, token_decay, beta, state, query_start, row_slot, rows, heads, \
                                                  kv_heads, dim, vdim, most, s)
     // Four channels a thread up to a key size of 64, then more channels a thread. (Key size 128, 2,048 tokens of 16 heads,
     // microseconds a token with the delta rule: 16 lanes of 8 channels 0.37, 32 lanes of 4 0.40, 8 lanes of 16 0.40, 4 lanes of

@@ -867,20 +867,23 @@ class CudaKernels:
         self._check(x)
         self._call("hb_activation", self._p(x), _code(x), ctypes.c_long(x.numel()), int(act))
 
-    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize) -> None:
-        self._check(chosen, weight, counts, z)
+    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize, bias=None) -> None:
+        """`bias` (float32 [experts] or None) is added to the logits before anything else."""
+        self._check(chosen, weight, counts, z, bias)
+        self._f32("route_top", bias)
         t, top = chosen.shape
         if z.dtype != torch.float32 or z.shape[0] != t or z.shape[1] < experts or weight.shape != (t, top) \
                 or weight.dtype != torch.float32 or counts.shape[0] < 2 * experts + 1:
             raise KernelError("route_top: z float32 [tokens, >= experts], chosen int32 and weight float32 [tokens, top], "
                               "counts int32 [2 experts + 1]")
         self._call("hb_route_top", self._i32(chosen, "chosen"), self._p(weight), self._i32(counts, "counts"), self._p(z),
-                   z.shape[1], t, int(experts), top, ctypes.c_float(scale), int(bool(renormalize)))
+                   self._p(bias), z.shape[1], t, int(experts), top, ctypes.c_float(scale), int(bool(renormalize)))
 
-    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize) -> None:
+    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize, bias=None) -> None:
         """`route_top` and `expert_rows` as one call (one launch for a few tokens). counts int32 [2 experts + 3] need not
         be zeroed; afterwards counts[2 experts + 1:] = (0, tokens)."""
-        self._check(chosen, weight, counts, place, token_of, z)
+        self._check(chosen, weight, counts, place, token_of, z, bias)
+        self._f32("route_rows", bias)
         t, top = chosen.shape
         if z.dtype != torch.float32 or z.shape[0] != t or z.shape[1] < experts or weight.shape != (t, top) \
                 or weight.dtype != torch.float32 or counts.shape[0] < 2 * experts + 3 or place.shape[0] != t * top \
@@ -888,7 +891,7 @@ class CudaKernels:
             raise KernelError("route_rows: z float32 [tokens, >= experts], chosen int32 and weight float32 [tokens, top], "
                               "counts int32 [2 experts + 3], place and token_of int32 [tokens * top]")
         self._call("hb_route_rows", self._i32(chosen, "chosen"), self._p(weight), self._i32(counts, "counts"),
-                   self._i32(place, "place"), self._i32(token_of, "token_of"), self._p(z), z.shape[1], t, int(experts), top,
+                   self._i32(place, "place"), self._i32(token_of, "token_of"), self._p(z), self._p(bias), z.shape[1], t, int(experts), top,
                    ctypes.c_float(scale), int(bool(renormalize)))
 
     def expert_rows(self, place, token_of, counts, chosen, experts) -> None:
@@ -990,19 +993,20 @@ class CudaKernels:
             if t is not None and t.dtype != torch.float32:
                 raise KernelError(f"{what}: 32-bit tensors expected, got {t.dtype}")
 
-    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows) -> None:
+    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows, token_decay=None) -> None:
         """The token-by-token update of a matrix state per head (csrc/api.h: hb_recurrent_scan)."""
-        self._check(out, qk, v, decay, head_decay, beta, state, rows.query_start, rows.row_slot)
-        self._f32("recurrent_scan", out, qk, v, decay, head_decay, beta, state)
+        self._check(out, qk, v, decay, head_decay, beta, state, rows.query_start, rows.row_slot, token_decay)
+        self._f32("recurrent_scan", out, qk, v, decay, head_decay, beta, state, token_decay)
         t, heads, vdim = v.shape
         kv_heads, dim = qk.shape[2], qk.shape[3]
         if qk.shape != (t, 2, kv_heads, dim) or out.shape != v.shape or state.shape[1:] != (heads, vdim, dim) \
                 or (decay is not None and decay.shape != (t, heads, dim)) or (beta is not None and beta.shape != (t, heads)) \
-                or (head_decay is not None and head_decay.shape != (heads,)):
+                or (head_decay is not None and head_decay.shape != (heads,)) \
+                or (token_decay is not None and token_decay.shape != (t, heads)):
             raise KernelError("recurrent_scan: qk [tokens, 2, kv_heads, dim], v and out [tokens, heads, vdim], state "
                               "[slots, heads, vdim, dim], decay [tokens, heads, dim] or head_decay [heads], beta [tokens, heads]")
         self._call("hb_recurrent_scan", self._p(out), self._p(qk), self._p(v), self._p(decay), self._p(head_decay),
-                   self._p(beta), self._p(state), self._i32(rows.query_start, "query_start"),
+                   self._p(token_decay), self._p(beta), self._p(state), self._i32(rows.query_start, "query_start"),
                    self._i32(rows.row_slot, "row_slot"), rows.n_rows, heads, kv_heads, dim, vdim,
                    int(getattr(rows, "max_q", 0) or 0))
 
@@ -1062,6 +1066,101 @@ class CudaKernels:
             raise KernelError("head_norm_gate: out and o [tokens, heads, vdim], weight [vdim], gate_mul of o's size")
         self._call("hb_head_norm_gate", self._p(out), self._p(o), _code(out), self._p(weight), self._p(gate_mul),
                    self._p(gate_pre), ctypes.c_long(ld), ctypes.c_float(eps), t, heads, vdim)
+
+    # ---- the matrix memory with exponential gates (csrc/mlstm.cu)
+    def mlstm_gates(self, out, pre, bias, cap, m_state, rows) -> None:
+        """out float32 [3, tokens, heads] = keep, take, exp(-m) from the gates' pre-activations `pre` float32 [tokens, >= 2
+        heads] (input gates, then forget gates), bias [2 heads]; m_state float32 [slots, heads] carries the maximum."""
+        self._check(out, pre, bias, m_state, rows.query_start, rows.row_slot)
+        self._f32("mlstm_gates", out, pre, m_state)
+        _, t, heads = out.shape
+        if out.shape[0] != 3 or pre.shape[0] != t or pre.shape[1] < 2 * heads or m_state.shape[1:] != (heads,) \
+                or (bias is not None and bias.shape != (2 * heads,)):
+            raise KernelError("mlstm_gates: out [3, tokens, heads], pre [tokens, >= 2 heads], bias [2 heads], m_state [slots, heads]")
+        self._call("hb_mlstm_gates", self._p(out), self._p(pre), pre.shape[1], self._p(bias),
+                   _code(bias) if bias is not None else 0, ctypes.c_float(cap), self._p(m_state),
+                   self._i32(rows.query_start, "query_start"), self._i32(rows.row_slot, "row_slot"), rows.n_rows, t, heads)
+
+    def mlstm_prepare(self, qk, v1, take, first, q_scale) -> None:
+        self._check(qk, v1, take, first)
+        self._f32("mlstm_prepare", qk, v1, take)
+        t, heads, vd1 = v1.shape
+        dim = qk.shape[3]
+        if qk.shape != (t, 2, heads, dim) or take.shape != (t, heads) or first.shape[0] != t \
+                or first.shape[1] < 2 * heads * dim + heads * (vd1 - 1):
+            raise KernelError("mlstm_prepare: qk [tokens, 2, heads, dim], v1 [tokens, heads, vdim + 1], take [tokens, heads], "
+                              "first [tokens, q | k | v | ...]")
+        self._call("hb_mlstm_prepare", self._p(qk), self._p(v1), self._p(take), self._p(first), _code(first), first.shape[1], t,
+                   heads, dim, vd1 - 1, ctypes.c_float(q_scale))
+
+    def mlstm_read_out(self, out, o1, floor, weight, gate_pre, eps, tiny) -> None:
+        self._check(out, o1, floor, weight)
+        self._f32("mlstm_read_out", o1, floor)
+        t, heads, vdim = out.shape
+        if o1.shape != (t, heads, vdim + 1) or floor.shape != (t, heads) or weight.shape != (heads * vdim,) \
+                or gate_pre.shape != (t, heads * vdim) or gate_pre.dtype != out.dtype or gate_pre.stride(1) != 1 \
+                or gate_pre.get_device() != self._index:
+            raise KernelError("mlstm_read_out: out [tokens, heads, vdim], o1 [tokens, heads, vdim + 1], floor [tokens, heads], "
+                              "weight [heads vdim], gate_pre [tokens, heads vdim] of out's dtype, innermost stride 1")
+        self._call("hb_mlstm_read_out", self._p(out), self._p(o1), self._p(floor), _code(out), self._p(weight), _code(weight),
+                   self._p(gate_pre), ctypes.c_long(gate_pre.stride(0)), ctypes.c_float(eps), ctypes.c_float(tiny), t, heads, vdim)
+
+    # ---- a norm on a sublayer's output and the average over the layers' results (csrc/elementwise.cu)
+    def out_norm_add(self, dst, src, y, bias, weight, eps, offset, hist=None, n_hist=0, coef=None, avg=None, cast=None) -> None:
+        """dst = src + N(y + bias) (y None: dst = src); with `hist` float32 [>= n_hist, rows, dim], whose entry n_hist - 1 is
+        dst: avg = sum_j coef[j] hist[j]; `cast` gets what goes on (avg, else dst) in its own dtype."""
+        self._check(dst, src, y, bias, weight, hist, coef, avg, cast)
+        self._f32("out_norm_add", dst, src, hist, coef, avg)
+        rows, dim = dst.shape
+        if src.shape != dst.shape or (y is not None and (y.shape != dst.shape or weight is None or weight.shape != (dim,))) \
+                or (bias is not None and bias.shape != (dim,)) or (cast is not None and cast.shape != dst.shape) \
+                or (hist is not None and (hist.shape[1:] != dst.shape or not 1 <= n_hist <= hist.shape[0] or coef is None
+                                          or coef.shape[0] < n_hist or avg is None or avg.shape != dst.shape)):
+            raise KernelError("out_norm_add: dst, src, y, avg, cast [rows, dim], bias and weight [dim], hist [n, rows, dim], coef [n]")
+        self._call("hb_out_norm_add", self._p(dst), self._p(src), self._p(y), _code(y) if y is not None else 0, self._p(bias),
+                   _code(bias) if bias is not None else 0, self._p(weight), _code(weight) if weight is not None else 0,
+                   ctypes.c_float(eps), ctypes.c_float(offset), self._p(hist), ctypes.c_long(rows * dim), int(n_hist),
+                   self._p(coef), self._p(avg), self._p(cast), _code(cast) if cast is not None else 0, rows, dim)
+
+    # ---- attention whose heads share their weights after the softmax (csrc/attention_talking.cu)
+    def qkv_talking_prepare(self, q_out, kv, keep, qkv, bias, q_weight, k_weight, eps, positions, table, rot_dims, interleaved,
+                            first, blend, write_index, heads, kv_heads, key_dim, value_dim) -> None:
+        self._check(q_out, kv, keep, qkv, bias, q_weight, k_weight, positions, table, first, blend, write_index)
+        self._f32("qkv_talking_prepare", keep, table, first, blend)
+        t = qkv.shape[0]
+        width = heads * key_dim + kv_heads * (key_dim + value_dim)
+        if qkv.shape != (t, width) or q_out.shape != (t, heads, key_dim) or q_out.dtype != qkv.dtype \
+                or (kv is not None and (kv.dtype != qkv.dtype or kv.shape[1] != kv_heads or kv.shape[3] != key_dim + value_dim
+                                        or write_index is None)) \
+                or (bias is not None and bias.shape != (width,)) \
+                or (q_weight is not None and (q_weight.shape != (key_dim,) or k_weight is None or k_weight.dtype != q_weight.dtype)) \
+                or (keep is not None and keep.shape != (t, kv_heads, value_dim)) \
+                or (first is not None and first.shape != (t, kv_heads, value_dim)) \
+                or (rot_dims and (table is None or table.shape[1] != rot_dims)):
+            raise KernelError("qkv_talking_prepare: qkv [tokens, q | k | v], q_out [tokens, heads, key_dim], cache [pages, "
+                              "kv_heads, page, key_dim + value_dim], keep and first float32 [tokens, kv_heads, value_dim]")
+        self._call("hb_qkv_talking_prepare", self._p(q_out), self._p(kv), self._p(keep), self._p(qkv), _code(qkv), self._p(bias),
+                   _code(bias) if bias is not None else 0, self._p(q_weight), self._p(k_weight),
+                   _code(q_weight) if q_weight is not None else 0, ctypes.c_float(eps), self._i32(positions, "positions"),
+                   self._p(table), int(rot_dims), table.shape[0] if table is not None else 0, int(bool(interleaved)),
+                   self._p(first), self._p(blend), self._i32(write_index, "write_index"),
+                   kv.shape[0] - 1 if kv is not None else 0, kv.shape[2] if kv is not None else 1, t, heads, kv_heads,
+                   key_dim, value_dim)
+
+    def attention_talking(self, out, q, kv, block_table, rows, scale, head_scale, chunk, window, talk) -> None:
+        self._check(out, q, kv, block_table, rows.row_slot, rows.query_start, rows.kv_len, head_scale, talk)
+        self._f32("attention_talking", head_scale, talk)
+        t, heads, kd = q.shape
+        vd = out.shape[2]
+        kv_heads = kv.shape[1]
+        if out.shape != (t, heads, vd) or kv.shape[3] != kd + vd or not (out.dtype == q.dtype == kv.dtype) \
+                or (head_scale is not None and head_scale.shape != (heads,)) or (talk is not None and talk.shape != (heads, heads)):
+            raise KernelError("attention_talking: q [tokens, heads, key_dim], out [tokens, heads, value_dim], cache [pages, "
+                              "kv_heads, page, key_dim + value_dim], head_scale [heads], talk [heads, heads]")
+        self._call("hb_attention_talking", self._p(out), self._p(q), self._p(kv), _code(q), self._i32(block_table, "block_table"),
+                   block_table.shape[1], self._i32(rows.row_slot, "row_slot"), self._i32(rows.query_start, "query_start"),
+                   self._i32(rows.kv_len, "kv_len"), rows.n_rows, t, heads, kv_heads, kd, vd, kv.shape[0] - 1, kv.shape[2],
+                   ctypes.c_float(scale), self._p(head_scale), int(chunk), int(window), self._p(talk))
 
     def feed_tokens(self, token_ids, last_tokens, rows, from_last) -> None:
         """token_ids[first token of row r] = last_tokens[slot of row r] for the rows whose `from_last` is set."""

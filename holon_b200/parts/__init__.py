@@ -1,8 +1,8 @@
 """Layers put together from parts: mixers, feed-forwards, norms, position encodings, blocks, and the model that
 arranges them by a run order."""
 from . import _builtin  # noqa: F401
-from .base import BuildContext, PagedKV, PagedLatent, Param, Part, Residual, SlotState, register_part, unregister_part
+from .base import BuildContext, PagedKV, PagedLatent, PagedRows, Param, Part, Residual, SlotState, register_part, unregister_part
 from .model import CacheEntry, LayerCache, Model
 
-__all__ = ["BuildContext", "CacheEntry", "LayerCache", "Model", "PagedKV", "PagedLatent", "Param", "Part", "Residual", "SlotState",
+__all__ = ["BuildContext", "CacheEntry", "LayerCache", "Model", "PagedKV", "PagedLatent", "PagedRows", "Param", "Part", "Residual", "SlotState",
            "register_part", "unregister_part"]

@@ -1,16 +1,16 @@
 """Registers the parts that ship with the framework."""
-from .attention import GQA
+from .attention import GQA, TalkingAttention
 from .base import register_part
-from .block import PreNorm
+from .block import OutNorm, PreNorm
 from .embedding import Embedding, Head, PairEmbedding
 from .experts import Experts
-from .feedforward import ClampedGLU, SwiGLU
+from .feedforward import MLP, ClampedGLU, SwiGLU
 from .hyper import Hyper
 from .latent import LatentAttention
 from .norm import RMSNorm
 from .parallel import ParallelBlock, SideBySide
 from .position import Rope
-from .recurrent import GatedDelta, Retention
+from .recurrent import MLSTM, GatedDelta, Retention
 
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
 register_part("position", "rope", Rope, replace=True)
@@ -28,3 +28,7 @@ register_part("mixer", "side_by_side", SideBySide, replace=True)
 register_part("ffn", "clamped_glu", ClampedGLU, replace=True)
 register_part("block", "parallel", ParallelBlock, replace=True)
 register_part("embed", "pair", PairEmbedding, replace=True)
+register_part("mixer", "talking", TalkingAttention, replace=True)
+register_part("mixer", "mlstm", MLSTM, replace=True)
+register_part("ffn", "mlp", MLP, replace=True)
+register_part("block", "outnorm", OutNorm, replace=True)

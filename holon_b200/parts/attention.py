@@ -19,7 +19,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import PartRef
-from .base import BuildContext, PagedKV, Part, take_link
+from .base import BuildContext, PagedKV, PagedRows, Part, take_link
 from .linear import Linear
 
 
@@ -105,3 +105,92 @@ class GQA(Part):
         else:
             k.paged_attention(o, q, cache.kv, cache.group.block_table, step.rows, self.scale, self.window)
         return self.o_proj.forward(o.view(t, self.heads * self.head_dim), link=take_link(step))
+
+
+class TalkingAttention(Part):
+    """Grouped-query attention whose heads share their softmax weights, with keys and values of unequal sizes.
+
+        s_g(i, j) = q_g(i) · k_kv(g)(j) · scale · temp[g],    p_g(i, ·) = softmax over the keys i sees,
+        out_h(i)  = Σ_j (Σ_g talk[h, g] p_g(i, j)) v_kv(h)(j)
+
+    `talk` [heads, heads] mixes the heads' weights after the softmax (`talking`), `temp` [heads] is a learned factor on each
+    head's scores (`head_temperature`); without them the mixer is plain attention. Which keys j ≤ i a query sees: with
+    `chunk` C only those of its own block of C positions (blocks counted from the sequence's first token, wherever a
+    prompt was cut), with `window` W only the last W. q and k carry biases (`biases`: q.b, k.b, v.b, o.b) and a per-head
+    RMS norm with one plain weight shared by the heads (`qk_eps` not None: q.norm, k.norm), then the position's
+    rotation. `blend`: "keep" leaves this layer's values (as projected, 32-bit) on the step under `blend_key` for later
+    layers; "mix" replaces this layer's values by (1 − λ) v + λ v_kept with the stored number `vmix`, and that is what the
+    cache holds; in both cases the stored `vmix` is loaded (the keeping layer does not use it). Scores, weights and
+    sums are 32-bit; q, keys and values are kept in the engine's dtype.
+
+    The cache keeps per token and kv head one row [key | value] (`PagedRows`). `forward_biased` returns the output
+    projection's product and its bias apart, for a block that adds the bias in its own sum."""
+
+    def __init__(self, ctx: BuildContext, *, heads: int, kv_heads: int, key_dim: int, value_dim: int, hidden: int,
+                 scale: float, position: PartRef | None = None, qk_eps: float | None = None, chunk: int = 0,
+                 window: int = 0, talking: bool = True, head_temperature: bool = True, biases: bool = True,
+                 blend: str | None = None, blend_key: str = "values", layer: int = 0) -> None:
+        super().__init__()
+        if heads % kv_heads:
+            raise ValueError(f"talking attention: {heads} heads are no multiple of {kv_heads} kv heads")
+        if blend not in (None, "keep", "mix"):
+            raise ValueError(f"talking attention: blend {blend!r}; known: None, 'keep', 'mix'")
+        self.ctx, self.heads, self.kv_heads, self.key_dim, self.value_dim = ctx, heads, kv_heads, key_dim, value_dim
+        self.scale, self.qk_eps, self.chunk, self.window = float(scale), qk_eps, int(chunk), int(window)
+        self.blend, self.blend_key = blend, blend_key
+        nq, nk, nv = heads * key_dim, kv_heads * key_dim, kv_heads * value_dim
+        self.first = self.add_child("first", Linear(ctx, "weight", hidden, {"q": nq, "k": nk, "v": nv}))
+        self.out = self.add_child("out", Linear(ctx, "weight", heads * value_dim, {"o": hidden}))
+        self.first_bias = self.out_bias = None
+        if biases:
+            self.first_bias = self.add_param("first_bias", (nq + nk + nv,), "matrix",
+                                             {"q.b": (0, nq), "k.b": (nq, nq + nk), "v.b": (nq + nk, nq + nk + nv)})
+            self.out_bias = self.add_param("o.b", (hidden,), "matrix")
+        self.q_gain = self.add_param("q.norm", (key_dim,), "coef") if qk_eps is not None else None
+        self.k_gain = self.add_param("k.norm", (key_dim,), "coef") if qk_eps is not None else None
+        self.talk = self.add_param("talk", (heads, heads), "coef") if talking else None
+        self.temp = self.add_param("temp", (heads,), "coef") if head_temperature else None
+        self.lam = self.add_param("vmix", (), "coef", optional=not blend)        # (a layer that does not blend may store it)
+        self.position = self.add_child("position", ctx.part(position, head_dim=key_dim)) if position else None
+
+    def loadables(self, prefix: str = ""):
+        for name, p, rows in super().loadables(prefix):
+            for child in ("first.", "out."):
+                if name.startswith(prefix + child):
+                    name = prefix + name[len(prefix + child):]
+            yield name, p, rows
+
+    def cache(self) -> PagedRows:
+        return PagedRows(self.kv_heads, self.key_dim, self.value_dim, self.window)
+
+    def slot_states(self):
+        return ()
+
+    def forward_biased(self, x: torch.Tensor, step, cache):
+        t, k, ctx = x.shape[0], self.ctx.kernels, self.ctx
+        heads, kvh, kd, vd = self.heads, self.kv_heads, self.key_dim, self.value_dim
+        qkv = self.first.forward(x)
+        q = ctx.empty(t, heads, kd)
+        keep = first = None
+        if self.blend == "keep":
+            keep = step.shared[self.blend_key] = ctx.empty(t, kvh, vd, dtype=torch.float32)
+        elif self.blend == "mix":
+            first = step.shared.get(self.blend_key)
+            if first is None:
+                raise RuntimeError(f"talking attention: no earlier layer of this step has left its values ({self.blend_key!r})")
+        pos = self.position
+        k.qkv_talking_prepare(q, cache.kv if cache.fills else None, keep, qkv,
+                              self.first_bias.tensor if self.first_bias else None,
+                              self.q_gain.tensor if self.q_gain else None, self.k_gain.tensor if self.k_gain else None,
+                              self.qk_eps or 0.0, step.positions, pos.table if pos else None, pos.rotary_dim if pos else 0,
+                              bool(pos and pos.interleaved), first, self.lam.tensor if first is not None else None,
+                              cache.group.write_index if cache.fills else None, heads, kvh, kd, vd)
+        o = ctx.empty(t, heads, vd)
+        k.attention_talking(o, q, cache.kv, cache.group.block_table, step.rows, self.scale,
+                            self.temp.tensor if self.temp else None, self.chunk, self.window,
+                            self.talk.tensor if self.talk else None)
+        return self.out.forward(o.view(t, heads * vd)), (self.out_bias.tensor if self.out_bias else None)
+
+    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+        y, bias = self.forward_biased(x, step, cache)
+        return y if bias is None else y + bias

@@ -21,12 +21,18 @@ class Param:
 
     `kind`: "matrix" (a product's weight, stored [out, in], kept in the engine's dtype), "gain" (a norm's weight:
     kept in the engine's dtype unless the file stores 32 bits, which stay 32 bits), "table" (embedding rows) or
-    "coef" (a few coefficients of a 32-bit computation: always kept in 32 bits)."""
+    "coef" (a few coefficients of a 32-bit computation: always kept in 32 bits). A shape of () is a single stored
+    number; it has one piece, itself. `optional`: a model folder may hold it or not, and the part does not read it."""
 
-    def __init__(self, name: str, shape: tuple[int, ...], kind: str, pieces: dict[str, tuple[int, int]] | None = None):
-        self.name, self.shape, self.kind = name, tuple(shape), kind
-        self.pieces = pieces or {name: (0, self.shape[0])}
+    def __init__(self, name: str, shape: tuple[int, ...], kind: str, pieces: dict[str, tuple[int, int]] | None = None,
+                 optional: bool = False):
+        self.name, self.shape, self.kind, self.optional = name, tuple(shape), kind, bool(optional)
+        self.pieces = pieces or {name: (0, self.shape[0] if self.shape else 1)}
         self.tensor: torch.Tensor | None = None
+
+    def piece_shape(self, rows: tuple[int, int]) -> tuple[int, ...]:
+        """The shape of the stored tensor that fills `rows` of this parameter."""
+        return (rows[1] - rows[0], *self.shape[1:]) if self.shape else ()
 
     def __repr__(self) -> str:
         return f"Param({self.name}, {self.shape}, {self.kind})"
@@ -37,10 +43,10 @@ class Part:
         self._params: dict[str, Param] = {}
         self._children: dict[str, "Part"] = {}
 
-    def add_param(self, name: str, shape, kind: str, pieces=None) -> Param:
+    def add_param(self, name: str, shape, kind: str, pieces=None, optional: bool = False) -> Param:
         if name in self._params:
             raise ValueError(f"parameter {name!r} declared twice")
-        self._params[name] = p = Param(name, tuple(shape), kind, pieces)
+        self._params[name] = p = Param(name, tuple(shape), kind, pieces, optional)
         return p
 
     def add_child(self, name: str, part: "Part") -> "Part":
@@ -97,6 +103,20 @@ class PagedLatent:
 
     def page_shape(self, page_size: int) -> tuple[int, ...]:
         return (page_size, self.rank + self.rot_dim)
+
+
+@dataclasses.dataclass(frozen=True)
+class PagedRows:
+    """Per token and kv head one row [key (key_dim) | value (value_dim)], in pages: for mixers whose keys and values
+    differ in size, and whose kernels read a token's key and value of all kv heads in one sweep. `window` as for PagedKV."""
+
+    kv_heads: int
+    key_dim: int
+    value_dim: int
+    window: int = 0
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        return (self.kv_heads, page_size, self.key_dim + self.value_dim)
 
 
 @dataclasses.dataclass(frozen=True)

@@ -1,8 +1,16 @@
 """Pre-norm residual block: h += mixer(input_norm(h)); h += ffn(post_norm(h))
 (std/holon_std/blocks/units.py:8-25). The sums are folded into the next norm's kernel: the block leaves the
 feed-forward's output pending on the stream. For the few rows of a decode step sum and norm move one kernel further
-up, into the product that ends the mixer or the feed-forward (base.Link, base.Scaled)."""
+up, into the product that ends the mixer or the feed-forward (base.Link, base.Scaled).
+
+OutNorm: the norm stands on a sublayer's OUTPUT, and the sublayers read the stream itself: x ← x + N(mixer(x)), then
+x ← x + N(ffn(x)). With `average` = n the block ends with an average over depth: with X_0 the embedding's rows and X_j
+what the j-th block before left (before ITS averaging), what goes on is Σ_j c[j] X_j over the n results so far, c the
+block's stored `depth` coefficients. The results of a step's blocks wait on the step (`step.shared`), 32-bit.
+"""
 from __future__ import annotations
+
+import torch
 
 from ..config.spec import PartRef
 from .base import BuildContext, Link, Part, Residual
@@ -43,3 +51,71 @@ class PreNorm(Part):
         if can is None or not getattr(reader, "takes_scaled", False) or not hasattr(norm, "weight"):
             return None
         return Link(stream, norm) if can(step.rows.n_tokens, stream.h.shape[1], norm) else None
+
+
+class OutNorm(Part):
+    """`average`: how many results this block averages (its own included; None: no averaging). `results`: how many the
+    step's blocks leave in all, the embedding's rows included (the first block of a step makes room for them)."""
+
+    KEY = "outnorm"                # step.shared: {"x": the stream's rows as the sublayers read them, "hist", "n"}
+
+    def __init__(self, ctx: BuildContext, *, layer: int, hidden: int, mixer: PartRef, ffn: PartRef | None, norm: PartRef,
+                 average: int | None = None, results: int = 0) -> None:
+        super().__init__()
+        if average is not None and not 1 <= average <= results:
+            raise ValueError(f"outnorm: an average over {average} of {results} results")
+        self.ctx, self.average, self.results = ctx, average, results
+        self.mixer_norm = self.add_child("mixer_norm", ctx.part(norm, dim=hidden))
+        self.mixer = self.add_child("mixer", ctx.part(mixer, layer=layer, hidden=hidden))
+        self.ffn_norm = self.ffn = None
+        if ffn is not None:
+            self.ffn_norm = self.add_child("ffn_norm", ctx.part(norm, dim=hidden))
+            self.ffn = self.add_child("ffn", ctx.part(ffn, layer=layer, hidden=hidden))
+        self.coef = self.add_param("depth", (average,), "coef") if average is not None else None
+
+    def _rows(self, t: int, hidden: int):
+        """A place for the stream's rows in the engine's dtype (None where that is 32-bit: the stream itself is read)."""
+        return None if self.ctx.dtype == torch.float32 else self.ctx.empty(t, hidden)
+
+    def forward(self, stream: Residual, step, cache, after=None) -> Residual:
+        k, ctx = self.ctx.kernels, self.ctx
+        t, hidden = stream.h.shape
+        if stream.delta is not None:                                     # (what a block of another kind left pending)
+            k.sum_into(stream.h, [(stream.delta, 1.0)])
+            stream.delta = None
+        stream.normed = stream.normed_by = None
+        state = step.shared.get(self.KEY)
+        if state is None:                                                # the first block of the step
+            state = step.shared[self.KEY] = {"x": None, "hist": None, "n": 0}
+            cast = self._rows(t, hidden)
+            if self.average is not None:
+                state["hist"] = ctx.empty(self.results, t, hidden, dtype=torch.float32)
+                k.out_norm_add(state["hist"][0], stream.h, None, None, None, 0.0, 0.0, cast=cast)
+                state["n"] = 1
+            elif cast is not None:
+                k.out_norm_add(stream.h, stream.h, None, None, None, 0.0, 0.0, cast=cast)
+            state["x"] = cast if cast is not None else stream.h
+        hist, n = state["hist"], state["n"]
+        if self.average is not None and (hist is None or n + 1 != self.average or n >= hist.shape[0]):
+            raise RuntimeError(f"outnorm: this block averages {self.average} results, the step holds {n} before it")
+        mixer, norm = self.mixer, self.mixer_norm
+        if hasattr(mixer, "forward_biased"):                             # the last product's bias rides in the norm's kernel
+            y, bias = mixer.forward_biased(state["x"], step, cache)
+        else:
+            y, bias = mixer.forward(state["x"], step, cache), None
+        own = hist[n] if self.average is not None else stream.h          # where this block's result is kept
+        src = stream.h
+        if self.ffn is not None:
+            mid = self._rows(t, hidden)
+            k.out_norm_add(own, src, y, bias, norm.weight.tensor, norm.eps, norm.offset, cast=mid)
+            y, bias, norm, src = self.ffn.forward(mid if mid is not None else own, step), None, self.ffn_norm, own
+        cast = self._rows(t, hidden)
+        if self.average is not None:
+            go = ctx.empty(t, hidden, dtype=torch.float32)
+            k.out_norm_add(own, src, y, bias, norm.weight.tensor, norm.eps, norm.offset, hist=hist, n_hist=n + 1,
+                           coef=self.coef.tensor, avg=go, cast=cast)
+            stream.h, state["n"] = go, n + 1
+        else:
+            k.out_norm_add(own, src, y, bias, norm.weight.tensor, norm.eps, norm.offset, cast=cast)
+        state["x"] = cast if cast is not None else stream.h
+        return stream

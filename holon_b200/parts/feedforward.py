@@ -2,7 +2,10 @@
 (std/holon_std/ffn/units.py:12-50; std/holon_std/ffn/reference.py:7-12).
 
 ClampedGLU: a gated unit whose inputs are clamped, with a bias on every projection: g = min(W_gate x + b, limit),
-u = clamp(W_up x + b, −limit, limit), y = g · sigmoid(alpha · g) · (u + 1), output W_down y + b."""
+u = clamp(W_up x + b, −limit, limit), y = g · sigmoid(alpha · g) · (u + 1), output W_down y + b.
+
+MLP: W_down act(W_up x), no gate and no bias; `activation` as the experts name theirs ("gelu_tanh": the tanh form of
+gelu, 0.5 z (1 + tanh(√(2/π) (z + 0.044715 z³))))."""
 from __future__ import annotations
 
 import torch
@@ -59,3 +62,26 @@ class ClampedGLU(Part):
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         y, bias = self.forward_biased(x, step)
         return y + bias
+
+
+class MLP(Part):
+    def __init__(self, ctx: BuildContext, *, inter: int, hidden: int, activation: str = "gelu_tanh", layer: int = 0) -> None:
+        super().__init__()
+        from .experts import ACTIVATIONS
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"mlp: activation {activation!r}; known: {sorted(ACTIVATIONS)}")
+        self.ctx, self.inter, self.act = ctx, inter, ACTIVATIONS[activation]
+        self.up = self.add_child("up_proj", Linear(ctx, "weight", hidden, {"up": inter}))
+        self.down = self.add_child("down_proj", Linear(ctx, "weight", inter, {"down": hidden}))
+
+    def loadables(self, prefix: str = ""):
+        for name, p, rows in super().loadables(prefix):
+            for child in ("up_proj.", "down_proj."):
+                if name.startswith(prefix + child):
+                    name = prefix + name[len(prefix + child):]
+            yield name, p, rows
+
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        z = self.up.forward(x)
+        self.ctx.kernels.activation(z, self.act)
+        return self.down.forward(z)

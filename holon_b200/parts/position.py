@@ -3,6 +3,8 @@ the mixer's fused kernel rotates q and k with it.
 
 Rope: inv_freq_i = θ^(−2i/rotary_dim), angle = position · inv_freq in 32-bit, half-split pairs (i, i + rotary_dim/2);
 dimensions past `rotary_dim` pass through (std/holon_std/ops/units.py:38-63; std/holon_std/ops/reference.py:21-30).
+With `interleaved` the pairs are neighbours (2i, 2i + 1) instead; the table is the same, and a mixer whose kernel knows
+both layouts passes the flag on.
 """
 from __future__ import annotations
 
@@ -12,11 +14,11 @@ from .base import BuildContext, Part
 
 
 class Rope(Part):
-    def __init__(self, ctx: BuildContext, *, theta: float, rotary_dim: int, head_dim: int) -> None:
+    def __init__(self, ctx: BuildContext, *, theta: float, rotary_dim: int, head_dim: int, interleaved: bool = False) -> None:
         super().__init__()
         if rotary_dim % 2 or not 0 <= rotary_dim <= head_dim:
             raise ValueError(f"rope: rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
-        self.theta, self.rotary_dim = float(theta), rotary_dim
+        self.theta, self.rotary_dim, self.interleaved = float(theta), rotary_dim, bool(interleaved)
         self.table = self.angles(ctx.max_positions).to(ctx.device)
 
     def angles(self, positions: int) -> torch.Tensor:

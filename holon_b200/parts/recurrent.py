@@ -14,6 +14,14 @@ q times dim^(−1/2); β = sigmoid(W_b x); g = exp(−exp(A_log) · softplus(W_a
 RMS norm with one weight shared by the heads, times sigmoid(W_g2 W_g1 x), then W_o. Query/key heads may be fewer than
 value heads (head h reads key head h // (heads / kv_heads)).
 
+`MLSTM`: a matrix memory with exponential gates. Per head and token a log input gate i = c tanh(a / c) and a log forget gate
+f = logsigmoid(c tanh(b / c)) (a, b: the gates' projections with biases, c = `gate_cap`), held in range by a running
+maximum m that starts at 0: m_t = max(f + m_(t−1), i); S_t = exp(f + m_(t−1) − m_t) S_(t−1) + exp(i − m_t) k vᵀ, and a
+normaliser n_t that follows the same rule with k alone; o = Sᵀq / (max(|n · q|, exp(−m)) + 1e-6) with q scaled by
+dim^(−1/2); each head's o divided by its root mean square, times a weight over all heads' channels, times sigmoid(W_g x),
+then W_o. n rides as one more value column of S (the value row gets a 1 behind it), so the update is the same scan with a
+decay per head and token; m is a second `SlotState`. The gates' projections leave their product in 32-bit.
+
 Everything that enters the recurrence is 32-bit (the scan's inputs are made in 32-bit from the first product's rows);
 the products themselves are the engine's. All first projections of a mixer are one merged product.
 """
@@ -33,7 +41,7 @@ class _MatrixState(Part):
         return None
 
     def _strip(self, prefix: str, name: str) -> str:
-        for child in ("first.", "low.", "out."):
+        for child in ("first.", "low.", "out.", "gates."):
             if name.startswith(prefix + child):
                 return prefix + name[len(prefix + child):]
         return name
@@ -140,4 +148,41 @@ class GatedDelta(_MatrixState):
         k.recurrent_scan(o, qk, v, decay, None, beta, cache.slots["state"], step.rows)
         y = ctx.empty(t, heads, vdim)
         k.head_norm_gate(y, o, self.gain.tensor, gate, None, self.eps)
+        return self.out.forward(y.view(t, heads * vdim))
+
+
+class MLSTM(_MatrixState):
+    TINY = 1e-6                           # added to the denominator of the read-out
+
+    def __init__(self, ctx: BuildContext, *, heads: int, dim: int, vdim: int, gate_cap: float, eps: float, hidden: int,
+                 layer: int = 0) -> None:
+        super().__init__()
+        if not gate_cap > 0:
+            raise ValueError("mlstm: gate_cap must be positive")
+        self.ctx, self.heads, self.dim, self.vdim = ctx, heads, dim, vdim
+        self.cap, self.eps = float(gate_cap), float(eps)
+        self.first = self.add_child("first", Linear(ctx, "weight", hidden, {
+            "q": heads * dim, "k": heads * dim, "v": heads * vdim, "g": heads * vdim}))
+        self.gates = self.add_child("gates", Linear(ctx, "weight", hidden, {"i": heads, "f": heads}))
+        self.gate_bias = self.add_param("gate_bias", (2 * heads,), "coef", {"i.b": (0, heads), "f.b": (heads, 2 * heads)})
+        self.gain = self.add_param("norm", (heads * vdim,), "coef")
+        self.out = self.add_child("out", Linear(ctx, "weight", heads * vdim, {"o": hidden}))
+
+    def slot_states(self):
+        return (SlotState("state", (self.heads, self.vdim + 1, self.dim)), SlotState("max", (self.heads,)))
+
+    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+        t, k, ctx, heads, dim, vdim = x.shape[0], self.ctx.kernels, self.ctx, self.heads, self.dim, self.vdim
+        f32 = torch.float32
+        first = self.first.forward(x)                                    # [t, q | k | v | g]
+        pre = self.gates.forward(x, out_dtype=f32)                       # [t, i | f] before bias, cap and logsigmoid
+        gates = ctx.empty(3, t, heads, dtype=f32)                        # keep, take, exp(-m)
+        k.mlstm_gates(gates, pre, self.gate_bias.tensor, self.cap, cache.slots["max"], step.rows)
+        qk, v1 = ctx.empty(t, 2, heads, dim, dtype=f32), ctx.empty(t, heads, vdim + 1, dtype=f32)
+        k.mlstm_prepare(qk, v1, gates[1], first, dim ** -0.5)
+        o1 = ctx.empty(t, heads, vdim + 1, dtype=f32)
+        k.recurrent_scan(o1, qk, v1, None, None, None, cache.slots["state"], step.rows, token_decay=gates[0])
+        y = ctx.empty(t, heads, vdim)
+        at = 2 * heads * dim + heads * vdim
+        k.mlstm_read_out(y, o1, gates[2], self.gain.tensor, first[:, at:at + heads * vdim], self.eps, self.TINY)
         return self.out.forward(y.view(t, heads * vdim))

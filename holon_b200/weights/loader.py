@@ -90,17 +90,17 @@ def load_weights(model, spec: ModelSpec, tensors: Iterable[tuple[str, torch.Tens
             twice.append(stored)
             continue
         p, (r0, r1) = targets[ours]
-        want = (r1 - r0, *p.shape[1:])
+        want = p.piece_shape((r0, r1))
         if tuple(tensor.shape) != want:
             shapes.append((stored, tensor.shape, want))
             filled.add(ours)                     # it is there, only wrong: not also "missing"
             continue
         if p.tensor is None:
             p.tensor = torch.empty(p.shape, dtype=_dtype_for(p.kind, tensor.dtype, dtype), device=device)
-        p.tensor[r0:r1].copy_(tensor)
+        (p.tensor[r0:r1] if p.shape else p.tensor).copy_(tensor)
         filled.add(ours)
-    missing = [names.stored(n) or n for n in targets if n not in filled]
+    missing = [names.stored(n) or n for n in targets if n not in filled and not targets[n][0].optional]
     if missing or unexpected or shapes or twice:
         raise WeightError(missing, unexpected, shapes, twice)
     model.finalize()
-    return sum(p.tensor.numel() * p.tensor.element_size() for _, p in model.params())
+    return sum(p.tensor.numel() * p.tensor.element_size() for _, p in model.params() if p.tensor is not None)

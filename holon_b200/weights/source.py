@@ -5,7 +5,7 @@ two files is an error (std/holon_std/weights/hf/source.py:49-115). Random: the r
 make tiny checkpoints with another library. Here every tensor is drawn from its own generator, seeded by
 (seed, stored name), so a tensor does not depend on which others are made, on their order, or on the device's
 memory: matrices and tables N(0, 0.02), norm weights 1 + N(0, 0.1), coefficients of 32-bit computations (kind "coef")
-near neutral values: a square matrix I + N(0, 0.05), a vector of n entries 1/n + N(0, 0.05).
+near neutral values: a square matrix I + N(0, 0.05), a vector of n entries 1/n + N(0, 0.05), a single number 0.5 + N(0, 0.05).
 """
 from __future__ import annotations
 
@@ -92,7 +92,7 @@ class RandomSource:
         spec = arch.recipe(arch.parse(self._config))
         model = Model(spec, BuildContext("meta", self.dtype, None, max_positions=1))
         names = NameMap(spec.weight_rules)
-        return [(names.stored(ours), (rows[1] - rows[0], *p.shape[1:]), p.kind) for ours, p, rows in model.loadables()]
+        return [(names.stored(ours), p.piece_shape(rows), p.kind) for ours, p, rows in model.loadables() if not p.optional]
 
     def tensors(self) -> Iterator[tuple[str, torch.Tensor]]:
         for name, shape, kind in self.table():
@@ -100,7 +100,10 @@ class RandomSource:
             x = torch.randn(shape, generator=g, dtype=torch.float32, device=self.device)
             if kind == "coef":
                 x = x.mul_(0.05)
-                x = x + (torch.eye(shape[0], device=self.device) if len(shape) == 2 and shape[0] == shape[1] else 1.0 / shape[0])
+                if len(shape) == 2 and shape[0] == shape[1]:
+                    x = x + torch.eye(shape[0], device=self.device)
+                else:
+                    x = x + (1.0 / shape[0] if shape else 0.5)
             else:
                 x = x.mul_(self.STD_GAIN).add_(1.0) if kind == "gain" else x.mul_(self.STD_MATRIX)
             yield name, x.to(self.dtype)

@@ -134,7 +134,7 @@ class RefKernels:
         g, u = g.clamp(max=limit), u.clamp(-limit, limit)
         out.copy_((g * torch.sigmoid(alpha * g) * (u + 1)).to(out.dtype))
 
-    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows):
+    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows, token_decay=None):
         t, heads, vdim = v.shape
         group = heads // qk.shape[2]
         qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
@@ -143,7 +143,8 @@ class RefKernels:
                 s = state[slots[b], h].T.clone()               # (kept column by column: [vdim, dim])
                 for i in range(qs[b], qs[b + 1]):
                     q, k = qk[i, 0, h // group], qk[i, 1, h // group]
-                    s = s * (decay[i, h][:, None] if decay is not None else head_decay[h])
+                    s = s * (decay[i, h][:, None] if decay is not None else
+                             token_decay[i, h] if token_decay is not None else head_decay[h])
                     u = v[i, h] if beta is None else beta[i, h] * (v[i, h] - s.T @ k)
                     s = s + torch.outer(k, u)
                     out[i, h] = s.T @ q
@@ -320,8 +321,9 @@ class RefKernels:
     def sigmoid_gate(self, o, g):
         o.copy_((o.float() * torch.sigmoid(g.float())).to(o.dtype))
 
-    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize):
-        s = torch.softmax(z[:, :experts].float(), dim=-1)
+    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize, bias=None):
+        z = z[:, :experts].float() + (bias.float() if bias is not None else 0.0)
+        s = torch.softmax(z, dim=-1)
         top = chosen.shape[1]
         order = torch.argsort(-s, dim=-1, stable=True)[:, :top]           # equal scores: the lower expert first
         w = torch.gather(s, 1, order)
@@ -331,9 +333,9 @@ class RefKernels:
         weight.copy_(w * scale)
         counts[:experts] += torch.bincount(order.reshape(-1), minlength=experts).to(torch.int32)
 
-    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize):
+    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize, bias=None):
         counts.zero_()
-        self.route_top(chosen, weight, counts, z, experts, scale, renormalize)
+        self.route_top(chosen, weight, counts, z, experts, scale, renormalize, bias)
         self.expert_rows(place, token_of, counts, chosen, experts)
         counts[2 * experts + 1], counts[2 * experts + 2] = 0, chosen.shape[0]
 
@@ -353,6 +355,8 @@ class RefKernels:
             return torch.relu(x) ** 2
         if act == 2:
             return torch.nn.functional.silu(x)
+        if act == 3:
+            return torch.nn.functional.gelu(x, approximate="tanh")
         return x
 
     def expert_linear(self, out, x, token_of, w, starts, act):
@@ -374,3 +378,117 @@ class RefKernels:
         if shared is not None:
             acc += torch.sigmoid(z[:, experts:experts + 1].float()) * shared.float()
         out.copy_(acc.to(out.dtype))
+
+    # ---- the matrix memory with exponential gates
+    def mlstm_gates(self, out, pre, bias, cap, m_state, rows):
+        heads = out.shape[2]
+        a = pre[:, :2 * heads].float() + (bias.float() if bias is not None else 0.0)
+        gi = cap * torch.tanh(a[:, :heads] / cap)
+        gf = torch.nn.functional.logsigmoid(cap * torch.tanh(a[:, heads:] / cap))
+        qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
+        for b in range(rows.n_rows):
+            m = m_state[slots[b]].clone()
+            for i in range(qs[b], qs[b + 1]):
+                new = torch.maximum(gf[i] + m, gi[i])
+                out[0, i], out[1, i], out[2, i] = torch.exp(gf[i] + m - new), torch.exp(gi[i] - new), torch.exp(-new)
+                m = new
+            m_state[slots[b]] = m
+
+    def mlstm_prepare(self, qk, v1, take, first, q_scale):
+        t, _, heads, dim = qk.shape
+        vdim = v1.shape[2] - 1
+        f, nq = first.float(), heads * dim
+        qk[:, 0] = f[:, :nq].view(t, heads, dim) * q_scale
+        qk[:, 1] = f[:, nq:2 * nq].view(t, heads, dim) * take[:, :, None]
+        v1[:, :, :vdim] = f[:, 2 * nq:2 * nq + heads * vdim].view(t, heads, vdim)
+        v1[:, :, vdim] = 1.0
+
+    def mlstm_read_out(self, out, o1, floor, weight, gate_pre, eps, tiny):
+        t, heads, vdim = out.shape
+        y = o1[:, :, :vdim] / (torch.maximum(o1[:, :, vdim].abs(), floor) + tiny)[:, :, None]
+        y = y * torch.rsqrt((y * y).mean(-1, keepdim=True) + eps)
+        y = y * weight.float().view(1, heads, vdim) * torch.sigmoid(gate_pre.float()).view(t, heads, vdim)
+        out.copy_(y.to(out.dtype))
+
+    # ---- a norm on a sublayer's output and the average over the layers' results
+    def out_norm_add(self, dst, src, y, bias, weight, eps, offset, hist=None, n_hist=0, coef=None, avg=None, cast=None):
+        x = src.float()
+        if y is not None:
+            z = y.float() + (bias.float() if bias is not None else 0.0)
+            x = x + z * torch.rsqrt((z * z).mean(-1, keepdim=True) + eps) * (weight.float() + offset)
+        if y is not None or dst.data_ptr() != src.data_ptr():
+            dst.copy_(x)
+        go = x
+        if hist is not None:
+            assert hist[n_hist - 1].data_ptr() == dst.data_ptr()
+            go = torch.zeros_like(x)
+            for j in range(n_hist - 1):
+                go = go + coef[j] * hist[j]
+            go = go + coef[n_hist - 1] * x
+            avg.copy_(go)
+        if cast is not None:
+            cast.copy_(go.to(cast.dtype))
+
+    # ---- attention whose heads share their weights after the softmax
+    def qkv_talking_prepare(self, q_out, kv, keep, qkv, bias, q_weight, k_weight, eps, positions, table, rot_dims, interleaved,
+                            first, blend, write_index, heads, kv_heads, key_dim, value_dim):
+        t = qkv.shape[0]
+        x = qkv.float() + (bias.float() if bias is not None else 0.0)
+        nq, nk = heads * key_dim, kv_heads * key_dim
+        q, k = x[:, :nq].view(t, heads, key_dim), x[:, nq:nq + nk].view(t, kv_heads, key_dim)
+        v = x[:, nq + nk:].view(t, kv_heads, value_dim)
+
+        def prepare(u, weight):
+            if weight is not None:
+                u = u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * weight.float()
+            if rot_dims:
+                cs = table[positions.long()]
+                half = rot_dims // 2
+                cos, sin = cs[:, None, :half], cs[:, None, half:]
+                u = u.clone()
+                if interleaved:
+                    a, b = u[..., 0:rot_dims:2].clone(), u[..., 1:rot_dims:2].clone()
+                    u[..., 0:rot_dims:2], u[..., 1:rot_dims:2] = a * cos - b * sin, b * cos + a * sin
+                else:
+                    a, b = u[..., :half].clone(), u[..., half:rot_dims].clone()
+                    u[..., :half], u[..., half:rot_dims] = a * cos - b * sin, b * cos + a * sin
+            return u
+
+        q_out.copy_(prepare(q, q_weight).to(q_out.dtype))
+        k = prepare(k, k_weight)
+        if keep is not None:
+            keep.copy_(v)
+        if blend is not None:
+            lam = float(blend)
+            v = (1.0 - lam) * v + lam * first
+        if kv is not None:
+            page = kv.shape[2]
+            w = write_index.long()
+            ok = (w >= 0) & (w < (kv.shape[0] - 1) * page)
+            rows = torch.cat((k, v), dim=-1).to(kv.dtype)
+            for i in torch.nonzero(ok).flatten().tolist():
+                kv[int(w[i]) // page, :, int(w[i]) % page] = rows[i]
+
+    def attention_talking(self, out, q, kv, block_table, rows, scale, head_scale, chunk, window, talk):
+        t, heads, kd = q.shape
+        vd, kvh, page = out.shape[2], kv.shape[1], kv.shape[2]
+        group = heads // kvh
+        qs, slots, lens = rows.query_start.tolist(), rows.row_slot.tolist(), rows.kv_len.tolist()
+        for b in range(rows.n_rows):
+            n, s, e = lens[b], qs[b], qs[b + 1]
+            pages = block_table[slots[b], :-(-n // page)].long()
+            held = kv[pages].float().permute(1, 0, 2, 3).reshape(kvh, -1, kd + vd)[:, :n]      # [kvh, n, kd + vd]
+            keys, values = held[..., :kd], held[..., kd:]
+            for i in range(s, e):
+                pos = n - e + i
+                lo = (pos // chunk) * chunk if chunk else 0
+                if window:
+                    lo = max(lo, pos - window + 1)
+                probs = torch.zeros(heads, pos + 1 - lo)
+                for g in range(heads):
+                    sc = (keys[g // group, lo:pos + 1] @ q[i, g].float()) * scale * (float(head_scale[g]) if head_scale is not None else 1.0)
+                    probs[g] = torch.softmax(sc, -1)
+                if talk is not None:
+                    probs = talk.float() @ probs
+                for h in range(heads):
+                    out[i, h] = (probs[h] @ values[h // group, lo:pos + 1]).to(out.dtype)
