@@ -1,0 +1,183 @@
+"""Tiny Tilarax configurations, model folders with weights that make faults show, and the comparison with the plain
+implementation (tests/plain_tilarax.py) that the CPU and GPU tests of this design share."""
+from __future__ import annotations
+
+import json
+
+import torch
+from safetensors.torch import load_file, save_file
+
+import plain_tilarax as plain
+
+
+def _att(heads, kv_heads, dim, vdim, size, sharpen, base, dims, v_mix=True):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": sharpen / dim ** 0.5, "v_mix": v_mix}
+    if size:
+        m["mask"] = {"size": size}
+    if dims:
+        m["rot"] = {"base": base, "dims": dims}
+    return m
+
+
+def _mem(heads, dim, vdim, cap):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": cap}
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def _moe(experts, top, ff):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+def _layer(kind, mixer, mlp):
+    return {"type": kind, "mixer": mixer, "mlp": mlp}
+
+
+def _model(width, vocab, eps, layers):
+    return json.loads(json.dumps({"architecture": "Tilarax", "width": width, "vocab": vocab, "norm": {"eps": eps},
+                                  "layers": layers}))
+
+
+# A: attention and memory layers in turn; blocks of 10 positions (longer than a page of 4, shorter than one of 64), a
+# rotation of a third of the channels, two kv heads for four heads, key and value sizes that differ, three layers that
+# blend values, dense and routed feed-forwards and a layer without one.
+_AA = _att(4, 2, 24, 16, 10, 4.0, 10000.0, 8)
+TA = _model(64, 211, 1e-5, [_layer("attention", _AA, _dense(96)), _layer("mlstm", _mem(2, 8, 12, 12.0), _moe(6, 2, 20)),
+                            _layer("attention", _AA, _moe(6, 2, 20)), _layer("mlstm", _mem(2, 8, 12, 12.0), None),
+                            _layer("attention", _AA, _moe(5, 3, 24))])
+# B: sizes that are multiples of nothing (width 72, heads of 20 and 28, an odd vocabulary), as many kv heads as heads,
+# every channel rotated, blocks of 7, one expert of three, one memory head, the memory layer first, one blending layer
+# only (it keeps its values for nobody), and a layer that blends nothing, rotates nothing and masks nothing.
+TB = _model(72, 157, 1e-6, [_layer("mlstm", _mem(1, 12, 20, 3.0), _dense(40)),
+                            _layer("attention", _att(3, 3, 20, 28, 7, 3.0, 500.0, 20), _moe(3, 1, 36)),
+                            _layer("attention", _att(6, 1, 12, 20, 0, 3.0, 0.0, 0, v_mix=False), None)])
+# C: blocks of 70 (over a page border of 64), eight heads on two kv heads, every expert chosen, a larger memory head
+# (sixteen key channels a thread), the first blending layer in the middle.
+TC = _model(128, 300, 1e-5, [_layer("attention", _att(8, 2, 32, 16, 70, 5.0, 1e6, 32, v_mix=False), _moe(4, 4, 32)),
+                             _layer("attention", _att(8, 2, 32, 16, 70, 5.0, 1e6, 32), None),
+                             _layer("mlstm", _mem(2, 96, 40, 8.0), _dense(64)),
+                             _layer("attention", _att(2, 2, 64, 16, 33, 5.0, 1e4, 2), _dense(64))])
+# One mechanism alone.
+T_ATT = _model(48, 97, 1e-5, [_layer("attention", _att(4, 2, 16, 12, 6, 3.0, 100.0, 16), None)])
+T_MEM = _model(48, 97, 1e-5, [_layer("mlstm", _mem(3, 16, 8, 5.0), None)])
+T_MOE = _model(48, 97, 1e-5, [_layer("mlstm", _mem(1, 4, 4, 5.0), _moe(7, 3, 16))])
+CONFIGS = {"a": TA, "b": TB, "c": TC, "att": T_ATT, "mem": T_MEM, "moe": T_MOE}
+
+
+def tensor_table(config):
+    """(stored name, shape) of every tensor of a model folder, from the configuration alone."""
+    w = config["width"]
+    out = [("embed", (config["vocab"], w)), ("final.norm", (w,))]
+    for i, layer in enumerate(config["layers"]):
+        m, mlp, p = layer["mixer"], layer.get("mlp"), f"l{i}."
+        out += [(p + "norm1", (w,)), (p + "dwa", (i + 2,))]
+        if layer["type"] == "attention":
+            nq, nk, nv = m["heads"] * m["dim"], m["kv_heads"] * m["dim"], m["kv_heads"] * m["vdim"]
+            out += [(p + "mix.q", (nq, w)), (p + "mix.q.b", (nq,)), (p + "mix.k", (nk, w)), (p + "mix.k.b", (nk,)),
+                    (p + "mix.v", (nv, w)), (p + "mix.v.b", (nv,)), (p + "mix.q.norm", (m["dim"],)),
+                    (p + "mix.k.norm", (m["dim"],)), (p + "mix.talk", (m["heads"], m["heads"])),
+                    (p + "mix.temp", (m["heads"],)), (p + "mix.o", (w, m["heads"] * m["vdim"])), (p + "mix.o.b", (w,))]
+            if m.get("v_mix"):
+                out.append((p + "mix.vmix", ()))
+        else:
+            nq, nv = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            out += [(p + "mix.q", (nq, w)), (p + "mix.k", (nq, w)), (p + "mix.v", (nv, w)), (p + "mix.g", (nv, w)),
+                    (p + "mix.o", (w, nv)), (p + "mix.norm", (nv,)), (p + "mix.i", (m["heads"], w)),
+                    (p + "mix.i.b", (m["heads"],)), (p + "mix.f", (m["heads"], w)), (p + "mix.f.b", (m["heads"],))]
+        if mlp is None:
+            continue
+        out.append((p + "norm2", (w,)))
+        if mlp["kind"] == "dense":
+            out += [(p + "mlp.up", (mlp["ff"], w)), (p + "mlp.down", (w, mlp["ff"]))]
+        else:
+            n, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+            out += [(p + "mlp.router", (n, w)), (p + "mlp.router.b", (n,))]
+            for e in range(n):
+                out += [(f"{p}mlp.e{e}.gate", (ff, w)), (f"{p}mlp.e{e}.up", (ff, w)), (f"{p}mlp.e{e}.down", (w, ff))]
+    return out
+
+
+def make_weights(config, seed: int):
+    """Random weights, rounded to bfloat16 (so that both sides read the same numbers). Products' weights are N(0, 1/in);
+    the embedding's rows have unit size, so with the configurations' score scales the scores spread over several units:
+    single keys stand out, and a wrong key, page or block edge moves the logits. The mixing matrix of the heads is far
+    from the identity, the heads' factors differ, the depth coefficients weigh early results visibly, the blend is near
+    a half, the router's biases decide some choices, and the gates' biases spread the memory's forgetting from a few
+    tokens to hundreds."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_table(config):
+        x = torch.randn(shape, generator=g, dtype=torch.float32)
+        tail = name.split(".", 1)[1] if "." in name else name
+        if name == "embed":
+            pass
+        elif tail in ("norm1", "norm2", "norm"):                        # (final.norm too: weights stored around zero)
+            x = 0.2 * x
+        elif tail == "dwa":
+            x = 1.0 / shape[0] + 0.3 * x
+        elif tail == "mix.talk":
+            x = torch.eye(shape[0]) + 0.4 * x
+        elif tail == "mix.temp":
+            x = 1.0 + 0.3 * x
+        elif tail == "mix.vmix":
+            x = 0.5 + 0.2 * x
+        elif tail in ("mix.q.norm", "mix.k.norm", "mix.norm"):
+            x = 1.0 + 0.1 * x
+        elif tail == "mix.f.b":
+            x = 2.0 + 2.0 * x
+        elif tail in ("mix.i.b", "mlp.router.b"):
+            pass
+        elif tail.endswith(".b"):
+            x = 0.3 * x
+        elif tail in ("mix.i", "mix.f"):
+            x = 2.0 * x / shape[1] ** 0.5
+        else:
+            x = x / shape[1] ** 0.5
+        out[name] = x.to(torch.bfloat16).contiguous()
+    return out
+
+
+def make_folder(tmp_path, name: str, seed: int = 0, config=None, weights=None):
+    config = config or CONFIGS[name]
+    folder = tmp_path / f"tilarax_{name}"
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(config))
+    save_file(weights if weights is not None else make_weights(config, seed), str(folder / "model.safetensors"))
+    return folder
+
+
+def read_folder(folder):
+    import pathlib
+    folder = pathlib.Path(folder)
+    return json.loads((folder / "config.json").read_text()), load_file(str(folder / "model.safetensors"))
+
+
+def exact_logits(folder, ids):
+    config, weights = read_folder(folder)
+    return plain.forward(weights, config, list(ids)).float()
+
+
+# The measure, per row: the distance from the plain implementation's 64-bit logits (mean taken off, root mean square
+# over the vocabulary) relative to the row's own spread. float32: every row within 2e-4. bfloat16: rounding alone leaves
+# rows of these models 0.005 to 0.04 away; every row within 0.1 and the median within 0.04. A wrong key, block edge,
+# state or slot moves the rows it touches by a good part of their spread.
+LIMITS = {"float32": 2e-4, "bfloat16": 0.1}
+
+
+def row_error(got, want):
+    d = got.double() - want.double()
+    d = d - d.mean()
+    spread = (want.double() - want.double().mean()).pow(2).mean().sqrt()
+    return float(d.pow(2).mean().sqrt() / spread)
+
+
+def compare(got, want, dtype):
+    """`got`: {(request, position): logits row}; `want`: {request: exact logits [tokens, vocab]}."""
+    assert got, "nothing to compare"
+    errors = sorted((row_error(row, want[rid][pos]), rid, pos) for (rid, pos), row in got.items())
+    worst = errors[-1]
+    assert worst[0] <= LIMITS[dtype], f"request {worst[1]} position {worst[2]}: error {worst[0]:.3g} of the row's spread"
+    if dtype == "bfloat16":
+        assert errors[len(errors) // 2][0] <= 0.04, f"the median row is {errors[len(errors) // 2][0]:.3g} of its spread off"
