@@ -113,6 +113,32 @@ KASOVIK_SIZES = {
 }
 
 
+def tilarax_config(width: int, heads: int, kv_heads: int, dim: int, vdim: int, chunk: int, rot: int, ff: int, experts: int,
+                   top: int, expert_ff: int, memory_heads: int, memory_dim: int, memory_vdim: int, layers: int,
+                   vocab: int = 32768) -> dict:
+    """A Tilarax model for `--only tilarax`: attention layers (talking heads, chunked mask, values blended with the first
+    layer's) and mLSTM layers in turn; layer 0 has a dense feed-forward, the others routed gated experts."""
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": chunk},
+                 "rot": {"base": 10000.0, "dims": rot}, "scale": dim ** -0.5, "v_mix": True}
+    memory = {"heads": memory_heads, "dim": memory_dim, "vdim": memory_vdim, "gate_cap": 15.0}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}}
+    return {"architecture": "Tilarax", "width": width, "vocab": vocab, "norm": {"eps": 1e-6},
+            "layers": [{"type": "mlstm" if i % 2 else "attention", "mixer": memory if i % 2 else attention,
+                        "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe} for i in range(layers)]}
+
+
+# Layers of the sizes of published decoders of 1.5 and 8 billion parameters (as Kasovik's), chunks of 1,024 and 2,048
+# positions, the matrix memory with a few large heads (its value size twice its key size), experts whose chosen ones
+# together have the dense feed-forward's size. Beside each the Kasovik model of `KASOVIK_SIZES` (attention beside a
+# matrix state: the closest design here) and the Qwen3 decoder of the same width, heads, key heads and layers.
+TILARAX_SIZES = {
+    "base": (dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=1024, rot=64, ff=6144, experts=32, top=4,
+                  expert_ff=1536, memory_heads=8, memory_dim=128, memory_vdim=256, layers=6), "base"),
+    "wide": (dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, chunk=2048, rot=64, ff=12288, experts=32, top=4,
+                  expert_ff=3072, memory_heads=8, memory_dim=256, memory_vdim=512, layers=6), "wide"),
+}
+
+
 def _find_number(data, key: str):
     """The first number stored under `key` anywhere in a nested JSON value (a dict under the key: its "value")."""
     if isinstance(data, dict):
@@ -568,7 +594,16 @@ def kasovik_run(args) -> dict:
     return beside_qwen3(args, "kasovik", KASOVIK_SIZES, kasovik_config, args.kasovik_sizes)
 
 
-def beside_qwen3(args, design: str, table: dict, make_config, chosen: str) -> dict:
+def tilarax_run(args) -> dict:
+    """The same for Tilarax beside the Kasovik model and the Qwen3 decoder of the same width, heads, key heads and layers.
+    Decode steps run over 1,536-token contexts: in the middle of a block of the mask (512 keys in sight with blocks of
+    1,024, 1,536 with blocks of 2,048), not at a block's start where a step sees next to nothing."""
+    table = {name: (ours, KASOVIK_SIZES[like][1], {"kasovik": kasovik_config(**KASOVIK_SIZES[like][0])})
+             for name, (ours, like) in TILARAX_SIZES.items()}
+    return beside_qwen3(args, "tilarax", table, tilarax_config, args.tilarax_sizes, context=1536)
+
+
+def beside_qwen3(args, design: str, table: dict, make_config, chosen: str, context: int = 2048) -> dict:
     import gc
     import torch
     from holon_b200.engine import Engine, EngineConfig
@@ -576,8 +611,8 @@ def beside_qwen3(args, design: str, table: dict, make_config, chosen: str) -> di
     out = {"only": design, "sizes": {}}
     steps = max(8, min(args.steps, 32))
     for name in (chosen.split(",") if chosen else table):
-        ours, theirs = table[name]
-        models = {design: make_config(**ours), "qwen3": dict(QWEN3_8B, **theirs)}
+        ours, theirs, *more = table[name]
+        models = {design: make_config(**ours), **(more[0] if more else {}), "qwen3": dict(QWEN3_8B, **theirs)}
         result = {}
         for which, cfg in models.items():
             engine = Engine(EngineConfig(model=f"random weights, {which} {name}", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -589,10 +624,10 @@ def beside_qwen3(args, design: str, table: dict, make_config, chosen: str) -> di
             ms = prefill_run(arm, 2048, repeats=3, seed=100)
             r["prefill"] = {"tokens": 2048, "ms": round(ms, 3), "tokens_per_s": round(2048 / ms * 1e3, 1)}
             for b in (1, 8):
-                d = decode_run(arm, b, 2048 + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
+                d = decode_run(arm, b, context + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
                 r[f"decode_b{b}"] = {"ms_per_step": round(d["device_ms"] / steps, 4), "tokens_per_s": round(d["tokens"] / d["device_ms"] * 1e3, 1)}
             if not args.no_kernels:
-                r["methods"] = step_tables(engine, 8, 2048, 2048)
+                r["methods"] = step_tables(engine, 8, context, 2048)
             result[which] = r
             engine.close()
             del engine, arm
@@ -714,6 +749,8 @@ def run_ours(args) -> dict:
         return rulorax_run(args)
     if args.only == "kasovik":
         return kasovik_run(args)
+    if args.only == "tilarax":
+        return tilarax_run(args)
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -836,7 +873,7 @@ def main() -> int:
                          "several passes should hold a few GB only (e.g. 0.03 with --layers 4 --batch 8)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt", "rulorax", "kasovik"),
+    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt", "rulorax", "kasovik", "tilarax"),
                     help="run one part only (for profiling a small case); the JSON line then lacks the other parts. "
                          "long_prompt: time to first token of a 30,000-token prompt behind three decoding requests; "
                          "sizes: the workloads of the Qwen3-32B and Qwen3-0.6B configurations (--sizes); "
@@ -845,6 +882,7 @@ def main() -> int:
     ap.add_argument("--sizes", default="32b", choices=("32b", "0.6b"), help="with --only sizes: which configuration")
     ap.add_argument("--rulorax-sizes", default="", help="with --only rulorax: which sizes (lite, small; default both)")
     ap.add_argument("--kasovik-sizes", default="", help="with --only kasovik: which sizes (base, wide; default both)")
+    ap.add_argument("--tilarax-sizes", default="", help="with --only tilarax: which sizes (base, wide; default both)")
     ap.add_argument("--no-points", action="store_true", help="leave out the points at other batch sizes and contexts")
     ap.add_argument("--no-kernels", action="store_true", help="leave out the per-kernel table")
     args = ap.parse_args()

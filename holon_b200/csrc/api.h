@@ -99,6 +99,16 @@ int hb_attention_prefill_tcgen05(void* out, const void* q, const void* kv, const
                                  const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,
                                  int rows, int q_tiles, int tokens, int heads, int kv_heads, int head_dim, int pages,
                                  int page_size, float scale, int window, int tile_q, const float* sinks, hb_stream stream);
+// The same kernel with its other forms as parameters. planes: 2 for a cache [pages, 2, kv_heads, page, 128], 1 for one whose
+// rows hold a token's key and value side by side [pages, kv_heads, page, 256]. value_heads: 1 (a query head weighs the
+// values of its own kv head; out [tokens, heads, 128]) or kv_heads (those of every kv head; out [tokens, heads * kv_heads,
+// 128], row h * kv_heads + c for query head h and kv head c). chunk > 0: a query at position i sees only keys
+// j >= floor(i / chunk) * chunk. head_scale (float [heads] without zeros, or null): a factor per head on the scores.
+int hb_attention_prefill_tcgen05_rows(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
+                                      const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,
+                                      int rows, int q_tiles, int tokens, int heads, int kv_heads, int head_dim, int pages,
+                                      int page_size, float scale, int window, int tile_q, const float* sinks, int planes,
+                                      int value_heads, int chunk, const float* head_scale, hb_stream stream);
 int hb_attention_tcgen05_status(unsigned int* status);
 
 // out[m, n] = sum_k x[m, k] * w[n, k], all float32, sums in a fixed order that does not depend on m's neighbours.
@@ -391,7 +401,14 @@ int hb_qkv_talking_prepare(void* q_out, void* kv, float* keep, const void* qkv, 
 int hb_attention_talking(void* out, const void* q, const void* kv, int dtype, const int32_t* block_table, int table_stride,
                          const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int rows, int tokens,
                          int heads, int kv_heads, int key_dim, int value_dim, int pages, int page_size, float scale,
-                         const float* head_scale, int chunk, int window, const float* talk, hb_stream stream);
+                         const float* head_scale, int chunk, int window, const float* talk, float* partial, int splits,
+                         hb_stream stream);
+// (splits > 1: every token's keys in that many parts, a block each, merged by a second kernel; partial: float
+// [tokens, splits, heads, kv_heads * value_dim + 2] of scratch.)
+// The mixing alone: out[t, h, :] = sum_g talk[h, g] wide[t, g, kv(h), :] for tokens token0 .. token0 + count - 1, wide
+// [tokens, heads, kv_heads, value_dim] (what hb_attention_prefill_tcgen05_rows leaves with value_heads = kv_heads).
+int hb_talking_mix(void* out, const void* wide, int dtype, int token0, int count, int heads, int kv_heads, int value_dim,
+                   const float* talk, hb_stream stream);
 
 #ifdef __cplusplus
 }

@@ -13,7 +13,12 @@
 // hb_qkv_talking_prepare  a first product's rows [q | k | v] -> bias, per-head RMSNorm of q and k, rotation, the value
 //                         blend with an earlier layer's values, q rows and the cache's [k | v] rows
 // hb_attention_talking    any sizes on CUDA cores, 32-bit arithmetic: the float32 engine's kernel, and the bfloat16
-//                         engine's for sizes the tensor-core kernel refuses
+//                         engine's for one-token rows and for sizes the tensor-core kernel refuses. With `splits` > 1 a
+//                         token's keys are cut into that many parts, a block each, and a second kernel merges the
+//                         parts (running maxima, sums, weighted values) before the heads are mixed: rows of one token
+//                         then fill the GPU.
+// hb_talking_mix          the mixing alone, for rows whose per-(query head, kv head) results the tensor-core prompt
+//                         kernel (csrc/attention_tcgen05.cu, value_heads = kv_heads) has left
 #include "common.cuh"
 
 __device__ __forceinline__ float load_any(const void* p, int f32, size_t i) {
@@ -136,20 +141,40 @@ extern "C" int hb_qkv_talking_prepare(void* q_out, void* kv, float* keep, const 
 // normalised results of all heads wait in shared memory, wide [heads][kv_heads * value_dim], and the block's threads then
 // mix them: out[h, d] = sum_g talk[h, g] wide[g][kv(h) value_dim + d] (talk null: the head's own result).
 #define TK_WARPS 16
-template <typename T, int EPL>
+// out[h, d] = sum_g talk[h, g] wide[g][kv(h) value_dim + d] for one token, by all threads of the block.
+template <typename T>
+__device__ __forceinline__ void talking_mix_store(T* __restrict__ out, const float* wide, const float* __restrict__ talk,
+                                                  size_t t, int heads, int kv_heads, int vd) {
+    const int group = heads / kv_heads, all = kv_heads * vd;
+    for (int e = threadIdx.x; e < heads * vd; e += blockDim.x) {
+        const int h = e / vd, d = e - h * vd, at = (h / group) * vd + d;
+        float o;
+        if (talk) {
+            o = 0.f;
+            for (int g = 0; g < heads; ++g) o = fmaf(talk[h * heads + g], wide[(size_t)g * all + at], o);
+        } else {
+            o = wide[(size_t)h * all + at];
+        }
+        out[(t * heads + h) * vd + d] = from_f32<T>(o);
+    }
+}
+
+// SPLIT: block (t, s) takes the s-th part of token t's keys and leaves, per head, its maximum, its sum and its weighted
+// values (not normalised) in partial [tokens, splits, heads, kv_heads value_dim + 2]; hb_talking_merge finishes.
+template <typename T, int EPL, bool SPLIT>
 __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ kv,
                                          const int32_t* __restrict__ block_table, int table_stride,
                                          const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
                                          const int32_t* __restrict__ kv_len, int rows, int heads, int kv_heads, int kd,
                                          int vd, int pages, int page_size, float scale,
                                          const float* __restrict__ head_scale, int chunk, int window,
-                                         const float* __restrict__ talk) {
+                                         const float* __restrict__ talk, float* __restrict__ partial) {
     extern __shared__ float tk_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int t = blockIdx.x;
     const int all = kv_heads * vd, rowlen = kd + vd;
-    float* wide = tk_smem;                                   // [heads][all]
-    float* qs = wide + (size_t)heads * all + (size_t)warp * kd;
+    float* wide = tk_smem;                                   // [heads][all] (not with SPLIT)
+    float* qs = wide + (SPLIT ? 0 : (size_t)heads * all) + (size_t)warp * kd;
 
     int lo = 0, hi = rows;                                   // the row b with query_start[b] <= t < query_start[b + 1]
     while (hi - lo > 1) {
@@ -164,7 +189,14 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
     int first = 0;
     if (live && chunk > 0) first = (pos / chunk) * chunk;
     if (live && window > 0) first = max(first, pos - window + 1);
+    int last = pos;                                          // this block's keys: first .. last
+    if (SPLIT && live) {
+        const int splits = gridDim.y, per = (((pos - first + splits) / splits) + 31) & ~31;
+        first += (int)blockIdx.y * per;
+        last = min(pos, first + per - 1);
+    }
     const long head_shift = (long)page_size * rowlen;        // from a kv head's row to the next kv head's row of the token
+    const bool vec16 = (kd & 7) == 0 && (rowlen & 7) == 0 && ((uintptr_t)kv & 15) == 0;
 
     long off[EPL];                                           // element e = lane + 32 i of [kv head][value]: where it lies
 #pragma unroll                                               // relative to the token's row of kv head 0
@@ -184,10 +216,10 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
             for (int d = lane; d < kd; d += 32) qs[d] = to_f32(qr[d]);
             __syncwarp();
             const int hk = g / (heads / kv_heads);
-            for (int j0 = first; j0 <= pos; j0 += 32) {
+            for (int j0 = first; j0 <= last; j0 += 32) {
                 const int j = j0 + lane;
                 long base = -1;                              // element offset of key j's row of kv head 0
-                if (j <= pos) {
+                if (j <= last) {
                     const int page = table[j / page_size];
                     if (page >= 0 && page < pages) base = (((long)page * kv_heads) * page_size + j % page_size) * rowlen;
                 }
@@ -195,7 +227,23 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
                 if (base >= 0) {
                     const T* kr = kv + base + hk * head_shift;
                     float dot = 0.f;
-                    for (int d = 0; d < kd; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
+                    if (sizeof(T) == 2 && vec16) {           // a row of bfloat16 in pieces of 16 bytes
+                        const uint4* k4 = (const uint4*)kr;
+                        float d4[4] = {0.f, 0.f, 0.f, 0.f};
+                        for (int c = 0; c < (kd >> 3); ++c) {
+                            const uint4 w = k4[c];
+                            const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+                            const float* qc = qs + 8 * c;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {    // (a bfloat16 is the upper half of the float32 of the same value)
+                                d4[i] = fmaf(qc[2 * i], __uint_as_float(u[i] << 16), d4[i]);
+                                d4[i] = fmaf(qc[2 * i + 1], __uint_as_float(u[i] & 0xffff0000u), d4[i]);
+                            }
+                        }
+                        dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+                    } else {
+                        for (int d = 0; d < kd; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
+                    }
                     s = dot * sc;
                 }
                 const float m_new = fmaxf(m, warp_max(s));
@@ -205,7 +253,7 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
                 m = m_new;
 #pragma unroll
                 for (int i = 0; i < EPL; ++i) acc[i] *= corr;
-                const int count = min(32, pos - j0 + 1);
+                const int count = min(32, last - j0 + 1);
                 for (int jj = 0; jj < count; ++jj) {
                     const float pj = __shfl_sync(0xffffffffu, p, jj);
                     const long bj = __shfl_sync(0xffffffffu, base, jj);
@@ -216,6 +264,16 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
                 }
             }
         }
+        if (SPLIT) {
+            float* part = partial + (((size_t)t * gridDim.y + blockIdx.y) * heads + g) * (all + 2);
+            if (lane == 0) { part[0] = m; part[1] = l; }
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) {
+                const int e = lane + 32 * i;
+                if (e < all) part[2 + e] = acc[i];
+            }
+            continue;
+        }
         const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
@@ -223,35 +281,88 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
             if (e < all) wide[(size_t)g * all + e] = acc[i] * inv;
         }
     }
+    if (SPLIT) return;
     __syncthreads();
-    const int group = heads / kv_heads;
-    for (int e = threadIdx.x; e < heads * vd; e += blockDim.x) {
-        const int h = e / vd, d = e - h * vd, at = (h / group) * vd + d;
-        float o;
-        if (talk) {
-            o = 0.f;
-            for (int g = 0; g < heads; ++g) o = fmaf(talk[h * heads + g], wide[(size_t)g * all + at], o);
-        } else {
-            o = wide[(size_t)h * all + at];
+    talking_mix_store<T>(out, wide, talk, (size_t)t, heads, kv_heads, vd);
+}
+
+// One block per token: the parts' maxima, sums and weighted values become each head's normalised results over every kv
+// head's values, then the heads are mixed. First a warp a head makes the parts' weights exp(m_s - m) / l (in a fixed
+// order over the parts), then every thread sums its (head, element) pairs over the parts: loads that do not wait for
+// one another.
+template <typename T>
+__global__ void talking_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, int splits, int heads,
+                                     int kv_heads, int vd, const float* __restrict__ talk) {
+    extern __shared__ float tk_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const size_t t = blockIdx.x;
+    const int all = kv_heads * vd;
+    float* wide = tk_smem;                                   // [heads][all]
+    float* share = wide + (size_t)heads * all;               // [heads][splits]
+    const float* mine = partial + t * splits * heads * (all + 2);
+    const size_t step = (size_t)heads * (all + 2);
+    for (int g = warp; g < heads; g += warps) {
+        const float* part = mine + (size_t)g * (all + 2);
+        float m = -INFINITY;
+        for (int s = lane; s < splits; s += 32) m = fmaxf(m, part[s * step]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int s0 = 0; s0 < splits; s0 += 32) {            // (a fixed order: part by part within a warp's sum)
+            const int s = s0 + lane;
+            const float ms = s < splits ? part[s * step] : -INFINITY;
+            const float w = ms > -INFINITY ? expf(ms - m) : 0.f;
+            if (s < splits) share[g * splits + s] = w;
+            l += warp_sum(s < splits ? part[s * step + 1] * w : 0.f);
         }
-        out[((size_t)t * heads + h) * vd + d] = from_f32<T>(o);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __syncwarp();
+        for (int s = lane; s < splits; s += 32) share[g * splits + s] *= inv;
     }
+    __syncthreads();
+    for (int i = threadIdx.x; i < heads * all; i += blockDim.x) {
+        const int g = i / all, e = i - g * all;
+        const float* part = mine + (size_t)g * (all + 2) + 2 + e;
+        const float* w = share + g * splits;
+        float a = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < splits; ++s) a = fmaf(part[s * step], w[s], a);
+        wide[i] = a;
+    }
+    __syncthreads();
+    talking_mix_store<T>(out, wide, talk, t, heads, kv_heads, vd);
+}
+
+// One block per token: wide_in [tokens, heads, value_heads, vd] (value_heads = kv_heads: every kv head's values under every
+// query head's weights; 1: one kv head in all) -> out[t, h, :] = sum_g talk[h, g] wide_in[t, g, kv(h), :].
+template <typename T>
+__global__ void talking_mix_kernel(T* __restrict__ out, const T* __restrict__ wide_in, int token0, int heads, int kv_heads,
+                                   int vd, const float* __restrict__ talk) {
+    extern __shared__ float tk_smem[];
+    const size_t t = (size_t)token0 + blockIdx.x;
+    const int n = heads * kv_heads * vd;
+    const T* src = wide_in + t * n;
+    for (int e = threadIdx.x; e < n; e += blockDim.x) tk_smem[e] = to_f32(src[e]);
+    __syncthreads();
+    talking_mix_store<T>(out, tk_smem, talk, t, heads, kv_heads, vd);
 }
 
 template <typename T>
 static int launch_talking(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
                           const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int rows, int tokens,
                           int heads, int kv_heads, int kd, int vd, int pages, int page_size, float scale,
-                          const float* head_scale, int chunk, int window, const float* talk, cudaStream_t s) {
+                          const float* head_scale, int chunk, int window, const float* talk, float* partial, int splits,
+                          cudaStream_t s) {
     const int all = kv_heads * vd;
     const int warps = heads < TK_WARPS ? heads : TK_WARPS;
-    const size_t smem = ((size_t)heads * all + (size_t)warps * kd) * sizeof(float);
-    if (smem > 200 * 1024) HB_REFUSE("attention_talking: %d heads over %d kv heads of %d values need %zu bytes of shared memory", heads, kv_heads, vd, smem);
+    const size_t wide_bytes = (size_t)heads * all * sizeof(float);
+    const size_t smem = (splits > 1 ? 0 : wide_bytes) + (size_t)warps * kd * sizeof(float);
+    if (wide_bytes + (size_t)warps * kd * sizeof(float) > 200 * 1024) HB_REFUSE("attention_talking: %d heads over %d kv heads of %d values need %zu bytes of shared memory", heads, kv_heads, vd, smem);
 #define HB_TALK(E) do { \
-        auto kernel = attention_talking_kernel<T, E>; \
+        auto kernel = splits > 1 ? attention_talking_kernel<T, E, true> : attention_talking_kernel<T, E, false>; \
         if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        kernel<<<tokens, warps * 32, smem, s>>>((T*)out, (const T*)q, (const T*)kv, block_table, table_stride, row_slot, \
-            query_start, kv_len, rows, heads, kv_heads, kd, vd, pages, page_size, scale, head_scale, chunk, window, talk); \
+        kernel<<<dim3(tokens, splits > 1 ? splits : 1), warps * 32, smem, s>>>((T*)out, (const T*)q, (const T*)kv, block_table, \
+            table_stride, row_slot, query_start, kv_len, rows, heads, kv_heads, kd, vd, pages, page_size, scale, head_scale, \
+            chunk, window, talk, partial); \
     } while (0)
     if (all <= 32) HB_TALK(1);
     else if (all <= 64) HB_TALK(2);
@@ -262,6 +373,12 @@ static int launch_talking(void* out, const void* q, const void* kv, const int32_
     else HB_REFUSE("attention_talking: %d kv heads of %d values are above 1024 numbers a head", kv_heads, vd);
 #undef HB_TALK
     HB_LAUNCH_CHECK("attention_talking");
+    if (splits > 1) {
+        const size_t merge_bytes = wide_bytes + (size_t)heads * splits * sizeof(float);
+        if (merge_bytes > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(talking_merge_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_bytes));
+        talking_merge_kernel<T><<<tokens, 512, merge_bytes, s>>>((T*)out, partial, splits, heads, kv_heads, vd, talk);
+        HB_LAUNCH_CHECK("talking_merge");
+    }
     return 0;
 }
 
@@ -269,16 +386,38 @@ extern "C" int hb_attention_talking(void* out, const void* q, const void* kv, in
                                     int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                     const int32_t* kv_len, int rows, int tokens, int heads, int kv_heads, int key_dim,
                                     int value_dim, int pages, int page_size, float scale, const float* head_scale, int chunk,
-                                    int window, const float* talk, hb_stream stream) {
+                                    int window, const float* talk, float* partial, int splits, hb_stream stream) {
     if (tokens == 0 || rows == 0) return 0;
+    if (splits > 1 && !partial) HB_REFUSE("attention_talking: %d parts need their scratch", splits);
+    if (splits > 65535) HB_REFUSE("attention_talking: %d parts", splits);
     if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_talking: %d heads are no multiple of %d kv heads", heads, kv_heads);
     if (key_dim < 1 || value_dim < 1 || chunk < 0 || window < 0) HB_REFUSE("attention_talking: key size %d, value size %d, chunk %d, window %d", key_dim, value_dim, chunk, window);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == HB_F32)
         return launch_talking<float>(out, q, kv, block_table, table_stride, row_slot, query_start, kv_len, rows, tokens, heads,
-                                     kv_heads, key_dim, value_dim, pages, page_size, scale, head_scale, chunk, window, talk, s);
+                                     kv_heads, key_dim, value_dim, pages, page_size, scale, head_scale, chunk, window, talk, partial, splits, s);
     if (dtype == HB_BF16)
         return launch_talking<bf16>(out, q, kv, block_table, table_stride, row_slot, query_start, kv_len, rows, tokens, heads,
-                                    kv_heads, key_dim, value_dim, pages, page_size, scale, head_scale, chunk, window, talk, s);
+                                    kv_heads, key_dim, value_dim, pages, page_size, scale, head_scale, chunk, window, talk, partial, splits, s);
     HB_REFUSE("attention_talking: dtype %d", dtype);
+}
+
+// out [tokens, heads, value_dim] for tokens token0 .. token0 + count - 1 from wide [tokens, heads, value_heads, value_dim]
+// (value_heads: kv_heads, or 1 with one kv head).
+extern "C" int hb_talking_mix(void* out, const void* wide, int dtype, int token0, int count, int heads, int kv_heads,
+                              int value_dim, const float* talk, hb_stream stream) {
+    if (count <= 0) return 0;
+    if (kv_heads < 1 || heads % kv_heads || value_dim < 1) HB_REFUSE("talking_mix: %d heads, %d kv heads, value size %d", heads, kv_heads, value_dim);
+    const size_t smem = (size_t)heads * kv_heads * value_dim * sizeof(float);
+    if (smem > 200 * 1024) HB_REFUSE("talking_mix: %zu bytes of shared memory a token", smem);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == HB_BF16) {
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(talking_mix_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        talking_mix_kernel<bf16><<<count, 256, smem, s>>>((bf16*)out, (const bf16*)wide, token0, heads, kv_heads, value_dim, talk);
+    } else if (dtype == HB_F32) {
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(talking_mix_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        talking_mix_kernel<float><<<count, 256, smem, s>>>((float*)out, (const float*)wide, token0, heads, kv_heads, value_dim, talk);
+    } else HB_REFUSE("talking_mix: dtype %d", dtype);
+    HB_LAUNCH_CHECK("talking_mix");
+    return 0;
 }

@@ -14,6 +14,12 @@
 // keys and values of a tile as four 64 x 64 boxes from the paged cache, found through the block table), warp 1 issues
 // the score MMAs and owns the tensor memory, warps 10 and 11 issue the groups' P V MMAs, warps 2-5 and 6-9 are the
 // groups' softmax and epilogue.
+// Two cache layouts: [pages, 2, kv_heads, page, 128] (keys and values in planes of their own) and, with `planes` 1,
+// [pages, kv_heads, page, 256] (a token's key and value of one kv head side by side). With `value_heads` V > 1 the grid
+// has heads * V columns: column h V + c weighs the values of kv head c with the weights of query head h (whose keys are
+// those of its own kv head), and writes row h V + c of out [tokens, heads V, 128]: what attention with mixed heads sums
+// up afterwards. `chunk` C > 0: a query at position i sees only keys j >= floor(i / C) C. `head_scale` (or null): a factor
+// per query head on its scores.
 // Keys past a row's length are masked; they are read (a page is loaded whole), which is safe because cache pools start
 // as zeros and only ever hold finite values. Every mbarrier wait is bounded (tcgen05.cuh).
 #include "tcgen05.cuh"
@@ -72,8 +78,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, bf16* __restrict__ out,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int rows, int heads,
-        int kv_heads, int pages, int page_size, float scale_log2, int window, int tile_q,
-        const float* __restrict__ sinks) {
+        int kv_heads, int pages, int page_size, float scale_log2_all, int window, int tile_q,
+        const float* __restrict__ sinks, int planes, int value_heads, int chunk, const float* __restrict__ head_scale) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_s = base, kv_s = q_s + AT_GROUPS * AT_Q_BYTES;
@@ -114,7 +120,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
     asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(slot));
 
     const int b = s_row;
-    const int h = blockIdx.x, hk = h / (heads / kv_heads);
+    const int h = (int)blockIdx.x / value_heads, hk = h / (heads / kv_heads);
+    const int hv = value_heads > 1 ? (int)blockIdx.x % value_heads : hk;      // the kv head whose values this CTA weighs
+    const float scale_log2 = head_scale ? scale_log2_all * head_scale[h] : scale_log2_all;
     int tile_lo = 0, t0 = 0, p0 = 0, n = 0, nq = 0;
     int g_tiles[AT_GROUPS] = {0, 0}, g_qn[AT_GROUPS] = {0, 0}, g_hi[AT_GROUPS] = {0, 0};
     if (b >= 0) {
@@ -122,7 +130,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         n = kv_len[b];
         t0 = query_start[b] + s_q0;
         p0 = n - nq + s_q0;                                          // position of the CTA's first query
-        const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+        int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+        if (chunk > 0) lo = max(lo, (p0 / chunk) * chunk);            // (the first query's block starts no later than the others')
         tile_lo = lo / AT_BN;
 #pragma unroll
         for (int g = 0; g < AT_GROUPS; ++g) {
@@ -148,14 +157,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
                 const int key0 = (tile_lo + j) * AT_BN;
                 int page = table[key0 / page_size];
                 page = page < 0 || page >= pages ? 0 : page;
-                const int k_row = ((page * 2) * kv_heads + hk) * page_size + key0 % page_size;   // row of the flattened cache
-                const int v_row = k_row + kv_heads * page_size;
+                const int k_row = ((page * planes) * kv_heads + hk) * page_size + key0 % page_size;   // row of the flattened cache
+                const int v_row = ((page * planes + planes - 1) * kv_heads + hv) * page_size + key0 % page_size;
+                const int v_x = planes == 1 ? AT_D : 0;                  // one plane: the value lies behind the key in its row
                 const uint32_t k_dst = kv_s + s * 2 * AT_KV_BYTES, v_dst = k_dst + AT_KV_BYTES;
                 mbar_expect_tx(kv_full0 + 8 * s, 2 * AT_KV_BYTES);
                 tma_load_2d(k_dst, &map_kv, kv_full0 + 8 * s, 0, k_row);
                 tma_load_2d(k_dst + AT_KV_BYTES / 2, &map_kv, kv_full0 + 8 * s, 64, k_row);
-                tma_load_2d(v_dst, &map_kv, kv_full0 + 8 * s, 0, v_row);
-                tma_load_2d(v_dst + AT_KV_BYTES / 2, &map_kv, kv_full0 + 8 * s, 64, v_row);
+                tma_load_2d(v_dst, &map_kv, kv_full0 + 8 * s, v_x, v_row);
+                tma_load_2d(v_dst + AT_KV_BYTES / 2, &map_kv, kv_full0 + 8 * s, v_x + 64, v_row);
             }
         }
     } else if (b >= 0 && (warp == 1 || warp >= AT_MMA_WARP1)) {
@@ -223,9 +233,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         const int r = q * 32 + lane;                                  // this thread's query row within the group
         const int pos = p0 + g * AT_BM + r;                           // and its position
         const int hi = g_hi[g], qn = g_qn[g], my_tiles = g_tiles[g];
+        const int first = chunk > 0 ? (pos / chunk) * chunk : 0;      // the first key of this query's block
+        const int last_first = chunk > 0 && qn > 0 ? ((p0 + g * AT_BM + qn - 1) / chunk) * chunk : 0;   // of the group's last query
         const uint32_t lane_t = tmem + g * 256 + ((uint32_t)(q * 32) << 16);
         const uint32_t o_t = lane_t + 2 * AT_BN;
         float m_used = -INFINITY, l = 0.f;                            // in log2 units; the maximum may lag by AT_RESCALE
+        const bool negative = scale_log2 < 0.f;                       // a negative factor of the head: the smallest score leads,
+        const uint32_t masked = negative ? 0x7f800000u : 0xff800000u; // and a masked one is +inf before the scale, -inf after
         bool ok = true;
         for (int j = 0; j < my_tiles && ok; ++j) {
             const int gb = g * 2 + (j & 1);
@@ -237,22 +251,32 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
             tc_ld32_nowait(lane_t + (j & 1) * AT_BN + 32, sr[1]);
             tc_ld_wait();
             const int key0 = (tile_lo + j) * AT_BN;
-            const bool edge = key0 + AT_BN - 1 > p0 + g * AT_BM || window > 0 || key0 + AT_BN > hi;
+            const bool edge = key0 + AT_BN - 1 > p0 + g * AT_BM || window > 0 || key0 + AT_BN > hi || key0 < last_first;
             if (edge) {
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = key0 + c * 32 + i;
-                        if (!(key <= pos && key < hi && (window <= 0 || pos - key < window))) sr[c][i] = 0xff800000u;   // -inf
+                        if (!(key <= pos && key < hi && key >= first && (window <= 0 || pos - key < window))) sr[c][i] = masked;
                     }
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64
+            float mx;                                                 // the score that is largest once scaled
+            if (!negative) {
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
+                for (int c = 0; c < 2; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
+                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            } else {
+                float mn4[4] = {INFINITY, INFINITY, INFINITY, INFINITY};
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mn4[i & 3] = fminf(mn4[i & 3], __uint_as_float(sr[c][i]));
+                mx = fminf(fminf(mn4[0], mn4[1]), fminf(mn4[2], mn4[3]));
+            }
             const float mt = mx * scale_log2;
             const bool grow = mt > m_used + AT_RESCALE || (m_used == -INFINITY && mt > -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {                      // rescale what is summed (whole warp: the TMEM ops are collective)
@@ -308,7 +332,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
             if (sinks && l > 0.f) l += at_ex2(fmaf(sinks[h], 1.4426950408889634f, -m_used));   // the sink: a weight without a value
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const bool keep = r < qn && my_tiles > 0 && l > 0.f;
-            bf16* o_row = out + ((size_t)(t0 + g * AT_BM + (r < qn ? r : 0)) * heads + h) * AT_D;
+            bf16* o_row = out + ((size_t)(t0 + g * AT_BM + (r < qn ? r : 0)) * gridDim.x + blockIdx.x) * AT_D;
 #pragma unroll
             for (int c = 0; c < AT_D / 32; ++c) {
                 uint32_t o[32];
@@ -366,7 +390,25 @@ extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void
                                             const int32_t* kv_len, int row0, int rows, int q_tiles, int tokens, int heads,
                                             int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
                                             int tile_q, const float* sinks, hb_stream stream) {
+    return hb_attention_prefill_tcgen05_rows(out, q, kv, block_table, table_stride, row_slot, query_start, kv_len, row0, rows,
+                                             q_tiles, tokens, heads, kv_heads, head_dim, pages, page_size, scale, window, tile_q,
+                                             sinks, 2, 1, 0, nullptr, stream);
+}
+
+// The same with the cache's layout (`planes` 2: keys and values in planes of their own; 1: side by side in one row), the
+// number of kv heads whose values every query head weighs (`value_heads` 1: its own; else kv_heads: all, out then has
+// heads * kv_heads rows a token), a mask in blocks of `chunk` positions (0: none) and a factor per head on the scores.
+extern "C" int hb_attention_prefill_tcgen05_rows(void* out, const void* q, const void* kv, const int32_t* block_table,
+                                                 int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                                                 const int32_t* kv_len, int row0, int rows, int q_tiles, int tokens, int heads,
+                                                 int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
+                                                 int tile_q, const float* sinks, int planes, int value_heads, int chunk,
+                                                 const float* head_scale, hb_stream stream) {
     if (rows <= row0 || q_tiles == 0) return 0;
+    if (planes != 1 && planes != 2) HB_REFUSE("attention_prefill_tcgen05: %d planes (1 or 2)", planes);
+    if (value_heads != 1 && value_heads != kv_heads) HB_REFUSE("attention_prefill_tcgen05: values of %d of %d kv heads (1 or all)", value_heads, kv_heads);
+    if (chunk < 0) HB_REFUSE("attention_prefill_tcgen05: blocks of %d positions", chunk);
+    if (sinks && value_heads != 1) HB_REFUSE("attention_prefill_tcgen05: sinks go with one value head a query head");
     if (tile_q != AT_BM && tile_q != AT_GROUPS * AT_BM) HB_REFUSE("attention_prefill_tcgen05: query tiles of %d (128 or 256)", tile_q);
     if (head_dim != AT_D) HB_REFUSE("attention_prefill_tcgen05: head_dim %d; this kernel is for %d", head_dim, AT_D);
     if (page_size % AT_BN) HB_REFUSE("attention_prefill_tcgen05: page size %d is no multiple of %d", page_size, AT_BN);
@@ -374,17 +416,17 @@ extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void
     if (q_tiles > 65535) HB_REFUSE("attention_prefill_tcgen05: %d query tiles in one step, above 65535", q_tiles);
     if (!(scale > 0.f)) HB_REFUSE("attention_prefill_tcgen05: the score scale must be positive");
     if ((((uintptr_t)q | (uintptr_t)kv | (uintptr_t)out) % 16) != 0) HB_REFUSE("attention_prefill_tcgen05: pointers must be 16-byte aligned");
-    const uint64_t kv_rows = (uint64_t)pages * 2 * kv_heads * page_size;
+    const uint64_t kv_rows = (uint64_t)pages * planes * kv_heads * page_size;
     if (kv_rows > 0x7fffffffull) HB_REFUSE("attention_prefill_tcgen05: the cache has %llu rows, above 2^31", (unsigned long long)kv_rows);
     CUtensorMap map_q, map_kv;
     int rc = encode_2d(&map_q, q, (uint64_t)heads * AT_D, (uint64_t)tokens, AT_BM, "q");
     if (rc) return rc;
-    rc = encode_2d(&map_kv, kv, AT_D, kv_rows, AT_BN, "the cache");
+    rc = encode_2d(&map_kv, kv, (uint64_t)AT_D * (planes == 1 ? 2 : 1), kv_rows, AT_BN, "the cache");
     if (rc) return rc;
     HB_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
-    prefill_tcgen05_kernel<<<dim3(heads, q_tiles), AT_THREADS, AT_SMEM, (cudaStream_t)stream>>>(
+    prefill_tcgen05_kernel<<<dim3(heads * value_heads, q_tiles), AT_THREADS, AT_SMEM, (cudaStream_t)stream>>>(
         map_q, map_kv, (bf16*)out, block_table, table_stride, row_slot, query_start, kv_len, row0, rows, heads, kv_heads,
-        pages, page_size, scale * 1.4426950408889634f, window, tile_q, sinks);
+        pages, page_size, scale * 1.4426950408889634f, window, tile_q, sinks, planes, value_heads, chunk, head_scale);
     HB_LAUNCH_CHECK("attention_prefill_tcgen05");
     return 0;
 }

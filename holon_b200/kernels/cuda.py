@@ -1147,7 +1147,12 @@ class CudaKernels:
                    kv.shape[0] - 1 if kv is not None else 0, kv.shape[2] if kv is not None else 1, t, heads, kv_heads,
                    key_dim, value_dim)
 
+    TALKING_SPLIT_KEYS = 64                   # the fewest keys a part of a one-token row's keys holds
+
     def attention_talking(self, out, q, kv, block_table, rows, scale, head_scale, chunk, window, talk) -> None:
+        """bfloat16 with keys and values of 128 numbers and pages of a multiple of 64 tokens: rows of several tokens run on the tcgen05 prompt kernel, every query head over the values of every kv
+        head, and a second kernel mixes the heads; rows of one token, other sizes and float32 run on CUDA cores, rows
+        of one token with their keys in parts where that fills more of the GPU."""
         self._check(out, q, kv, block_table, rows.row_slot, rows.query_start, rows.kv_len, head_scale, talk)
         self._f32("attention_talking", head_scale, talk)
         t, heads, kd = q.shape
@@ -1157,10 +1162,36 @@ class CudaKernels:
                 or (head_scale is not None and head_scale.shape != (heads,)) or (talk is not None and talk.shape != (heads, heads)):
             raise KernelError("attention_talking: q [tokens, heads, key_dim], out [tokens, heads, value_dim], cache [pages, "
                               "kv_heads, page, key_dim + value_dim], head_scale [heads], talk [heads, heads]")
-        self._call("hb_attention_talking", self._p(out), self._p(q), self._p(kv), _code(q), self._i32(block_table, "block_table"),
-                   block_table.shape[1], self._i32(rows.row_slot, "row_slot"), self._i32(rows.query_start, "query_start"),
-                   self._i32(rows.kv_len, "kv_len"), rows.n_rows, t, heads, kv_heads, kd, vd, kv.shape[0] - 1, kv.shape[2],
-                   ctypes.c_float(scale), self._p(head_scale), int(chunk), int(window), self._p(talk))
+        common = (self._i32(block_table, "block_table"), block_table.shape[1], self._i32(rows.row_slot, "row_slot"),
+                  self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"))
+        n_rows, n_tokens = rows.n_rows, t
+        fast = q.dtype == torch.bfloat16 and kd == 128 and vd == 128 and kv.shape[2] % 64 == 0 and scale > 0 \
+            and self.attention_bf16 == "fast" \
+            and self.prefill_attention == "tcgen05" and rows.n_rows > rows.n_decode
+        if fast:
+            value_heads = kv_heads if talk is not None else 1
+            wide = out if value_heads == 1 and talk is None else torch.empty(t, heads * value_heads, vd, dtype=q.dtype, device=q.device)
+            tile_q, tiles = 256, self._query_tiles(rows, 256)
+            if self.prefill_tile == 128 or (self.prefill_tile is None and 4 * heads * value_heads * tiles < 3 * self.sms):
+                tile_q, tiles = 128, self._query_tiles(rows, 128)
+            self._call("hb_attention_prefill_tcgen05_rows", self._p(wide), self._p(q), self._p(kv), *common, rows.n_decode,
+                       rows.n_rows, tiles, t, heads, kv_heads, kd, kv.shape[0] - 1, kv.shape[2], ctypes.c_float(scale), int(window),
+                       tile_q, self._p(None), 1, value_heads, int(chunk), self._p(head_scale))
+            if wide is not out:
+                self._call("hb_talking_mix", self._p(out), self._p(wide), _code(q), rows.n_decode, t - rows.n_decode, heads,
+                           kv_heads, vd, self._p(talk))
+            n_rows = n_tokens = rows.n_decode                         # (rows of one token come first in a step)
+            if not n_rows:
+                return
+        splits, partial = 1, None
+        if n_rows == rows.n_decode and n_rows:                        # rows of one token only: their keys in parts
+            keys = min(x for x in (rows.max_kv, chunk, window) if x > 0)
+            splits = max(1, min(-(-2 * self.sms // n_tokens), -(-keys // self.TALKING_SPLIT_KEYS), 64))
+            if splits > 1:
+                partial = torch.empty(n_tokens * splits * heads * (kv_heads * vd + 2), dtype=torch.float32, device=q.device)
+        self._call("hb_attention_talking", self._p(out), self._p(q), self._p(kv), _code(q), *common, n_rows, n_tokens, heads,
+                   kv_heads, kd, vd, kv.shape[0] - 1, kv.shape[2], ctypes.c_float(scale), self._p(head_scale), int(chunk),
+                   int(window), self._p(talk), self._p(partial), splits)
 
     def feed_tokens(self, token_ids, last_tokens, rows, from_last) -> None:
         """token_ids[first token of row r] = last_tokens[slot of row r] for the rows whose `from_last` is set."""

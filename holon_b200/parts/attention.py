@@ -160,6 +160,15 @@ class TalkingAttention(Part):
                     name = prefix + name[len(prefix + child):]
             yield name, p, rows
 
+    @property
+    def plan_group(self):
+        return "talking", self.heads, self.kv_heads, self.key_dim, self.value_dim, self.chunk, self.window
+
+    def capture_plan(self, step, max_model_len: int):
+        """What the attention kernels pin for a step that is captured as a CUDA graph (see base.Part)."""
+        plan = getattr(self.ctx.kernels, "attention_capture_plan", None)
+        return plan(step.rows, max_model_len) if plan is not None else None
+
     def cache(self) -> PagedRows:
         return PagedRows(self.kv_heads, self.key_dim, self.value_dim, self.window)
 

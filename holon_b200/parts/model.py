@@ -85,6 +85,7 @@ class Model(Part):
 
     def trunk(self, step):
         """The residual stream after the last run, for every token of the step."""
+        step.shared = {}                                      # (a step may pass twice: eagerly, then under a graph's capture)
         if getattr(self.embed, "wants_step", False):          # an embedding that reads positions, rows or carried state
             stream = self.embed.forward(step.token_ids, step)
         else:

