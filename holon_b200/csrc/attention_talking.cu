@@ -161,8 +161,20 @@ __device__ __forceinline__ void talking_mix_store(T* __restrict__ out, const flo
 
 // SPLIT: block (t, s) takes the s-th part of token t's keys and leaves, per head, its maximum, its sum and its weighted
 // values (not normalised) in partial [tokens, splits, heads, kv_heads value_dim + 2]; hb_talking_merge finishes.
-template <typename T, int EPL, bool SPLIT>
-__global__ void attention_talking_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ kv,
+// VEC: a lane owns runs of four neighbouring numbers (4 lane + 128 i .. + 3) and loads each run at once; the sizes must
+// then be multiples of four and the pool aligned (the launcher sees to it). Else it owns every 32nd number.
+__device__ __forceinline__ void load_run4(const bf16* p, float v[4]) {
+    const uint2 w = *(const uint2*)p;                        // (a bfloat16 is the upper half of the float32 of the same value)
+    v[0] = __uint_as_float(w.x << 16); v[1] = __uint_as_float(w.x & 0xffff0000u);
+    v[2] = __uint_as_float(w.y << 16); v[3] = __uint_as_float(w.y & 0xffff0000u);
+}
+__device__ __forceinline__ void load_run4(const float* p, float v[4]) {
+    const float4 w = *(const float4*)p;
+    v[0] = w.x; v[1] = w.y; v[2] = w.z; v[3] = w.w;
+}
+
+template <typename T, int EPL, bool SPLIT, bool VEC>
+__global__ void __launch_bounds__(TK_WARPS * 32) attention_talking_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ kv,
                                          const int32_t* __restrict__ block_table, int table_stride,
                                          const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
                                          const int32_t* __restrict__ kv_len, int rows, int heads, int kv_heads, int kd,
@@ -201,7 +213,7 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
     long off[EPL];                                           // element e = lane + 32 i of [kv head][value]: where it lies
 #pragma unroll                                               // relative to the token's row of kv head 0
     for (int i = 0; i < EPL; ++i) {
-        const int e = lane + 32 * i;
+        const int e = VEC ? 4 * lane + 128 * (i >> 2) + (i & 3) : lane + 32 * i;
         off[i] = e < all ? (long)(e / vd) * head_shift + kd + e % vd : -1;
     }
     for (int g = warp; g < heads; g += warps) {
@@ -254,13 +266,24 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
 #pragma unroll
                 for (int i = 0; i < EPL; ++i) acc[i] *= corr;
                 const int count = min(32, last - j0 + 1);
-                for (int jj = 0; jj < count; ++jj) {
+#pragma unroll 4
+                for (int jj = 0; jj < count; ++jj) {         // (no branch inside: the loads of several keys fly together)
                     const float pj = __shfl_sync(0xffffffffu, p, jj);
-                    const long bj = __shfl_sync(0xffffffffu, base, jj);
-                    if (bj < 0) continue;
+                    long bj = __shfl_sync(0xffffffffu, base, jj);
+                    bj = bj < 0 ? 0 : bj;                    // (a key without a page has weight 0: any row of finite numbers serves)
+                    if (VEC) {
 #pragma unroll
-                    for (int i = 0; i < EPL; ++i)
-                        if (off[i] >= 0) acc[i] = fmaf(pj, to_f32(kv[bj + off[i]]), acc[i]);
+                        for (int r = 0; r < EPL / 4; ++r) {  // (a run past the row's end reads the row's start: its sums are dropped)
+                            float v[4];
+                            load_run4(kv + bj + (off[4 * r] >= 0 ? off[4 * r] : 0), v);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) acc[4 * r + k] = fmaf(pj, v[k], acc[4 * r + k]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < EPL; ++i)
+                            if (off[i] >= 0) acc[i] = fmaf(pj, to_f32(kv[bj + off[i]]), acc[i]);
+                    }
                 }
             }
         }
@@ -269,7 +292,7 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
             if (lane == 0) { part[0] = m; part[1] = l; }
 #pragma unroll
             for (int i = 0; i < EPL; ++i) {
-                const int e = lane + 32 * i;
+                const int e = VEC ? 4 * lane + 128 * (i >> 2) + (i & 3) : lane + 32 * i;
                 if (e < all) part[2 + e] = acc[i];
             }
             continue;
@@ -277,7 +300,7 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
         const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
-            const int e = lane + 32 * i;
+            const int e = VEC ? 4 * lane + 128 * (i >> 2) + (i & 3) : lane + 32 * i;
             if (e < all) wide[(size_t)g * all + e] = acc[i] * inv;
         }
     }
@@ -286,50 +309,53 @@ __global__ void attention_talking_kernel(T* __restrict__ out, const T* __restric
     talking_mix_store<T>(out, wide, talk, (size_t)t, heads, kv_heads, vd);
 }
 
-// One block per token: the parts' maxima, sums and weighted values become each head's normalised results over every kv
-// head's values, then the heads are mixed. First a warp a head makes the parts' weights exp(m_s - m) / l (in a fixed
-// order over the parts), then every thread sums its (head, element) pairs over the parts: loads that do not wait for
-// one another.
+// One block per (token, output head h): out[h, d] = sum over query heads g and parts s of
+// talk[h, g] exp(m_gs - m_g) / l_g * part_gs[kv(h) value_dim + d], m_g and l_g the merged maximum and sum of head g.
+// The factors of all (g, s) are made first (a thread a head, its parts in order), then the threads share the pairs
+// (g, s) out in slices, a value channel each, and the slices are added in order: loads that do not wait for one another.
+#define TM_THREADS 256
 template <typename T>
 __global__ void talking_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, int splits, int heads,
                                      int kv_heads, int vd, const float* __restrict__ talk) {
     extern __shared__ float tk_smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const size_t t = blockIdx.x;
-    const int all = kv_heads * vd;
-    float* wide = tk_smem;                                   // [heads][all]
-    float* share = wide + (size_t)heads * all;               // [heads][splits]
-    const float* mine = partial + t * splits * heads * (all + 2);
-    const size_t step = (size_t)heads * (all + 2);
-    for (int g = warp; g < heads; g += warps) {
-        const float* part = mine + (size_t)g * (all + 2);
-        float m = -INFINITY;
-        for (int s = lane; s < splits; s += 32) m = fmaxf(m, part[s * step]);
-        m = warp_max(m);
-        float l = 0.f;
-        for (int s0 = 0; s0 < splits; s0 += 32) {            // (a fixed order: part by part within a warp's sum)
-            const int s = s0 + lane;
-            const float ms = s < splits ? part[s * step] : -INFINITY;
-            const float w = ms > -INFINITY ? expf(ms - m) : 0.f;
-            if (s < splits) share[g * splits + s] = w;
-            l += warp_sum(s < splits ? part[s * step + 1] * w : 0.f);
+    const int h = blockIdx.y, tid = threadIdx.x;
+    const int all = kv_heads * vd, c = h / (heads / kv_heads), pairs = heads * splits;
+    float* w = tk_smem;                                      // [splits][heads]: sums, then factors
+    float* mm = w + pairs;                                   // [splits][heads]: maxima, then exp(m_gs - m_g)
+    float* red = mm + pairs;                                 // [slices][vd]
+    const float* mine = partial + t * (size_t)pairs * (all + 2);
+    for (int i = tid; i < pairs; i += TM_THREADS) { mm[i] = mine[(size_t)i * (all + 2)]; w[i] = mine[(size_t)i * (all + 2) + 1]; }
+    __syncthreads();
+    for (int g = tid; g < heads; g += TM_THREADS) {
+        float m = -INFINITY, l = 0.f;
+        for (int s = 0; s < splits; ++s) m = fmaxf(m, mm[s * heads + g]);
+        for (int s = 0; s < splits; ++s) {
+            const float ms = mm[s * heads + g], e = ms > -INFINITY ? expf(ms - m) : 0.f;
+            l = fmaf(w[s * heads + g], e, l);
+            mm[s * heads + g] = e;
         }
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        __syncwarp();
-        for (int s = lane; s < splits; s += 32) share[g * splits + s] *= inv;
+        const float f = (talk ? talk[h * heads + g] : (g == h ? 1.f : 0.f)) * (l > 0.f ? 1.f / l : 0.f);
+        for (int s = 0; s < splits; ++s) w[s * heads + g] = mm[s * heads + g] * f;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < heads * all; i += blockDim.x) {
-        const int g = i / all, e = i - g * all;
-        const float* part = mine + (size_t)g * (all + 2) + 2 + e;
-        const float* w = share + g * splits;
+    const int slices = vd >= TM_THREADS ? 1 : TM_THREADS / vd;
+    const int slice = vd >= TM_THREADS ? 0 : tid / vd;
+    if (slice < slices) {
+        for (int d = vd >= TM_THREADS ? tid : tid - slice * vd; d < vd; d += TM_THREADS) {
+            const float* col = mine + 2 + c * vd + d;
+            float a = 0.f;
+#pragma unroll 8
+            for (int i = slice; i < pairs; i += slices) a = fmaf(col[(size_t)i * (all + 2)], w[i], a);
+            red[slice * vd + d] = a;
+        }
+    }
+    __syncthreads();
+    for (int d = tid; d < vd; d += TM_THREADS) {
         float a = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < splits; ++s) a = fmaf(part[s * step], w[s], a);
-        wide[i] = a;
+        for (int k = 0; k < slices; ++k) a += red[k * vd + d];
+        out[(t * heads + h) * vd + d] = from_f32<T>(a);
     }
-    __syncthreads();
-    talking_mix_store<T>(out, wide, talk, t, heads, kv_heads, vd);
 }
 
 // One block per token: wide_in [tokens, heads, value_heads, vd] (value_heads = kv_heads: every kv head's values under every
@@ -341,9 +367,11 @@ __global__ void talking_mix_kernel(T* __restrict__ out, const T* __restrict__ wi
     const size_t t = (size_t)token0 + blockIdx.x;
     const int n = heads * kv_heads * vd;
     const T* src = wide_in + t * n;
+    float* mix = tk_smem + n;                                // the mixing matrix beside the token's rows
     for (int e = threadIdx.x; e < n; e += blockDim.x) tk_smem[e] = to_f32(src[e]);
+    if (talk) for (int e = threadIdx.x; e < heads * heads; e += blockDim.x) mix[e] = talk[e];
     __syncthreads();
-    talking_mix_store<T>(out, tk_smem, talk, t, heads, kv_heads, vd);
+    talking_mix_store<T>(out, tk_smem, talk ? mix : nullptr, t, heads, kv_heads, vd);
 }
 
 template <typename T>
@@ -357,8 +385,10 @@ static int launch_talking(void* out, const void* q, const void* kv, const int32_
     const size_t wide_bytes = (size_t)heads * all * sizeof(float);
     const size_t smem = (splits > 1 ? 0 : wide_bytes) + (size_t)warps * kd * sizeof(float);
     if (wide_bytes + (size_t)warps * kd * sizeof(float) > 200 * 1024) HB_REFUSE("attention_talking: %d heads over %d kv heads of %d values need %zu bytes of shared memory", heads, kv_heads, vd, smem);
+    const bool vec = vd % 4 == 0 && kd % 4 == 0 && ((uintptr_t)kv % (4 * sizeof(T))) == 0;   // runs of four never cross a kv head
 #define HB_TALK(E) do { \
-        auto kernel = splits > 1 ? attention_talking_kernel<T, E, true> : attention_talking_kernel<T, E, false>; \
+        auto kernel = splits > 1 ? (vec && E >= 4 ? attention_talking_kernel<T, E, true, (E >= 4)> : attention_talking_kernel<T, E, true, false>) \
+                                 : (vec && E >= 4 ? attention_talking_kernel<T, E, false, (E >= 4)> : attention_talking_kernel<T, E, false, false>); \
         if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         kernel<<<dim3(tokens, splits > 1 ? splits : 1), warps * 32, smem, s>>>((T*)out, (const T*)q, (const T*)kv, block_table, \
             table_stride, row_slot, query_start, kv_len, rows, heads, kv_heads, kd, vd, pages, page_size, scale, head_scale, \
@@ -374,9 +404,10 @@ static int launch_talking(void* out, const void* q, const void* kv, const int32_
 #undef HB_TALK
     HB_LAUNCH_CHECK("attention_talking");
     if (splits > 1) {
-        const size_t merge_bytes = wide_bytes + (size_t)heads * splits * sizeof(float);
+        const int slices = vd >= TM_THREADS ? 1 : TM_THREADS / vd;
+        const size_t merge_bytes = ((size_t)2 * heads * splits + (size_t)slices * vd) * sizeof(float);
         if (merge_bytes > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(talking_merge_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_bytes));
-        talking_merge_kernel<T><<<tokens, 512, merge_bytes, s>>>((T*)out, partial, splits, heads, kv_heads, vd, talk);
+        talking_merge_kernel<T><<<dim3(tokens, heads), TM_THREADS, merge_bytes, s>>>((T*)out, partial, splits, heads, kv_heads, vd, talk);
         HB_LAUNCH_CHECK("talking_merge");
     }
     return 0;
@@ -408,7 +439,7 @@ extern "C" int hb_talking_mix(void* out, const void* wide, int dtype, int token0
                               int value_dim, const float* talk, hb_stream stream) {
     if (count <= 0) return 0;
     if (kv_heads < 1 || heads % kv_heads || value_dim < 1) HB_REFUSE("talking_mix: %d heads, %d kv heads, value size %d", heads, kv_heads, value_dim);
-    const size_t smem = (size_t)heads * kv_heads * value_dim * sizeof(float);
+    const size_t smem = ((size_t)heads * kv_heads * value_dim + (size_t)heads * heads) * sizeof(float);
     if (smem > 200 * 1024) HB_REFUSE("talking_mix: %zu bytes of shared memory a token", smem);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == HB_BF16) {
