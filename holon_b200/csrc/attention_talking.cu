@@ -309,13 +309,131 @@ __global__ void __launch_bounds__(TK_WARPS * 32) attention_talking_kernel(T* __r
     talking_mix_store<T>(out, wide, talk, (size_t)t, heads, kv_heads, vd);
 }
 
+// Rows of one token, staged: block (t, s) brings tiles of R1_KEYS keys of its part, the rows [key | value] of every kv
+// head, into shared memory once (16 bytes a load, rows padded against bank conflicts), and all heads work on them:
+// a thread a (head, key) pair for the scores, a warp a head for the running maximum and sum, and for the values a thread
+// owns a run of four numbers of the kv_heads * value_dim wide row under HPT heads (their weights come from shared memory
+// four at a time). Leaves the same partial results as the kernel above with SPLIT; hb's merge kernel finishes.
+#define R1_KEYS 32
+#define R1_THREADS 512
+template <typename T, int HPT>
+__global__ void __launch_bounds__(R1_THREADS) talking_rows1_kernel(
+        const T* __restrict__ q, const T* __restrict__ kv, const int32_t* __restrict__ block_table, int table_stride,
+        const int32_t* __restrict__ row_slot, const int32_t* __restrict__ kv_len, int heads, int kv_heads, int kd, int vd,
+        int pages, int page_size, float scale, const float* __restrict__ head_scale, int chunk, int window,
+        float* __restrict__ partial) {
+    extern __shared__ __align__(16) unsigned char r1_smem[];
+    constexpr int PER16 = 16 / (int)sizeof(T);               // numbers in 16 bytes
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t = blockIdx.x, splits = gridDim.y;
+    const int all = kv_heads * vd, rowlen = kd + vd, rowpad = rowlen + PER16, group = heads / kv_heads;
+    float* qs = (float*)r1_smem;                             // [heads][kd]
+    float* sc = qs + (size_t)heads * kd;                     // [R1_KEYS][heads]: scores, then weights
+    float* st = sc + R1_KEYS * heads;                        // [3][heads]: maximum, sum, this tile's correction
+    T* tile = (T*)(qs + (((size_t)heads * (kd + R1_KEYS + 3) + 3) & ~(size_t)3));   // [kv_heads][R1_KEYS][rowpad], 16-byte aligned
+    const int n = kv_len[t], pos = n - 1;                    // (row t holds one token: the last of its n)
+    const bool live = n > 0;
+    int first = 0, last = pos;
+    if (live && chunk > 0) first = (pos / chunk) * chunk;
+    if (live && window > 0) first = max(first, pos - window + 1);
+    if (live) {
+        const int per = (((pos - first + splits) / splits) + 31) & ~31;
+        first += (int)blockIdx.y * per;
+        last = min(pos, first + per - 1);
+    }
+    for (int i = tid; i < heads * kd; i += R1_THREADS) qs[i] = to_f32(q[(size_t)t * heads * kd + i]);
+    for (int i = tid; i < heads; i += R1_THREADS) { st[i] = -INFINITY; st[heads + i] = 0.f; }
+    const int runs = all >> 2;                               // threads a head group
+    const int r = tid % runs, g0 = (tid / runs) * HPT;       // this thread's run of values and its first head
+    const int e0 = 4 * r, c = e0 / vd;                       // the run's first number in the wide row, its kv head
+    const bool owner = g0 + HPT <= heads;
+    float acc[HPT][4];
+#pragma unroll
+    for (int h = 0; h < HPT; ++h)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[h][k] = 0.f;
+    const int32_t* table = block_table + (size_t)row_slot[t] * table_stride;
+    const int chunks16 = rowlen / PER16;                     // 16-byte pieces a row
+    for (int j0 = first; live && j0 <= last; j0 += R1_KEYS) {
+        __syncthreads();                                     // (the tile before is read; first pass: qs and st are written)
+        for (int i = tid; i < kv_heads * R1_KEYS * chunks16; i += R1_THREADS) {
+            const int piece = i % chunks16, j = (i / chunks16) % R1_KEYS, ck = i / (chunks16 * R1_KEYS);
+            const int key = j0 + j;
+            uint4 w = make_uint4(0u, 0u, 0u, 0u);            // keys past the part, or without a page: zeros
+            if (key <= last) {
+                const int page = table[key / page_size];
+                if (page >= 0 && page < pages)
+                    w = *(const uint4*)(kv + (((size_t)page * kv_heads + ck) * page_size + key % page_size) * rowlen + piece * PER16);
+            }
+            *(uint4*)(tile + ((size_t)ck * R1_KEYS + j) * rowpad + piece * PER16) = w;
+        }
+        __syncthreads();
+        for (int pair = tid; pair < heads * R1_KEYS; pair += R1_THREADS) {      // scores: a warp a head, a lane a key
+            const int g = pair / R1_KEYS, j = pair % R1_KEYS;
+            const T* kr = tile + ((size_t)(g / group) * R1_KEYS + j) * rowpad;
+            const float* qg = qs + (size_t)g * kd;
+            float d4[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int x = 0; x < kd; x += 4) {
+                float v[4];
+                load_run4(kr + x, v);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) d4[k] = fmaf(qg[x + k], v[k], d4[k]);
+            }
+            const float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+            sc[j * heads + g] = j0 + j <= last ? dot * scale * (head_scale ? head_scale[g] : 1.f) : -INFINITY;
+        }
+        __syncthreads();
+        for (int g = warp; g < heads; g += R1_THREADS / 32) {                    // maximum and sum: a warp a head
+            const float sv = sc[lane * heads + g];
+            const float m_old = st[g], m_new = fmaxf(m_old, warp_max(sv));
+            const float corr = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
+            const float pv = sv > -INFINITY ? expf(sv - m_new) : 0.f;
+            const float sum = warp_sum(pv);
+            sc[lane * heads + g] = pv;
+            if (lane == 0) { st[g] = m_new; st[heads + g] = st[heads + g] * corr + sum; st[2 * heads + g] = corr; }
+        }
+        __syncthreads();
+        if (owner) {
+#pragma unroll
+            for (int h = 0; h < HPT; ++h) {
+                const float corr = st[2 * heads + g0 + h];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[h][k] *= corr;
+            }
+            const T* vr = tile + (size_t)c * R1_KEYS * rowpad + kd + (e0 - c * vd);
+#pragma unroll 4
+            for (int j = 0; j < R1_KEYS; ++j) {
+                float v[4];
+                load_run4(vr + (size_t)j * rowpad, v);
+                const float* pj = sc + j * heads + g0;
+#pragma unroll
+                for (int h = 0; h < HPT; ++h) {
+                    const float w = pj[h];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc[h][k] = fmaf(w, v[k], acc[h][k]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (owner) {
+#pragma unroll
+        for (int h = 0; h < HPT; ++h) {
+            float* part = partial + (((size_t)t * splits + blockIdx.y) * heads + g0 + h) * (all + 2);
+            if (r == 0) { part[0] = st[g0 + h]; part[1] = st[heads + g0 + h]; }
+            *(float2*)(part + 2 + e0) = make_float2(acc[h][0], acc[h][1]);          // (rows of all + 2 numbers: 8-byte aligned)
+            *(float2*)(part + 4 + e0) = make_float2(acc[h][2], acc[h][3]);
+        }
+    }
+}
+
 // One block per (token, output head h): out[h, d] = sum over query heads g and parts s of
 // talk[h, g] exp(m_gs - m_g) / l_g * part_gs[kv(h) value_dim + d], m_g and l_g the merged maximum and sum of head g.
 // The factors of all (g, s) are made first (a thread a head, its parts in order), then the threads share the pairs
 // (g, s) out in slices, a value channel each, and the slices are added in order: loads that do not wait for one another.
-#define TM_THREADS 256
+#define TM_THREADS 1024
 template <typename T>
-__global__ void talking_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, int splits, int heads,
+__global__ void __launch_bounds__(TM_THREADS) talking_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, int splits, int heads,
                                      int kv_heads, int vd, const float* __restrict__ talk) {
     extern __shared__ float tk_smem[];
     const size_t t = blockIdx.x;
@@ -345,7 +463,7 @@ __global__ void talking_merge_kernel(T* __restrict__ out, const float* __restric
         for (int d = vd >= TM_THREADS ? tid : tid - slice * vd; d < vd; d += TM_THREADS) {
             const float* col = mine + 2 + c * vd + d;
             float a = 0.f;
-#pragma unroll 8
+#pragma unroll 16
             for (int i = slice; i < pairs; i += slices) a = fmaf(col[(size_t)i * (all + 2)], w[i], a);
             red[slice * vd + d] = a;
         }
@@ -375,6 +493,17 @@ __global__ void talking_mix_kernel(T* __restrict__ out, const T* __restrict__ wi
 }
 
 template <typename T>
+static int launch_talking_merge(void* out, const float* partial, int splits, int tokens, int heads, int kv_heads, int vd,
+                                const float* talk, cudaStream_t s) {
+    const int slices = vd >= TM_THREADS ? 1 : TM_THREADS / vd;
+    const size_t merge_bytes = ((size_t)2 * heads * splits + (size_t)slices * vd) * sizeof(float);
+    if (merge_bytes > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(talking_merge_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_bytes));
+    talking_merge_kernel<T><<<dim3(tokens, heads), TM_THREADS, merge_bytes, s>>>((T*)out, partial, splits, heads, kv_heads, vd, talk);
+    HB_LAUNCH_CHECK("talking_merge");
+    return 0;
+}
+
+template <typename T>
 static int launch_talking(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
                           const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int rows, int tokens,
                           int heads, int kv_heads, int kd, int vd, int pages, int page_size, float scale,
@@ -386,6 +515,27 @@ static int launch_talking(void* out, const void* q, const void* kv, const int32_
     const size_t smem = (splits > 1 ? 0 : wide_bytes) + (size_t)warps * kd * sizeof(float);
     if (wide_bytes + (size_t)warps * kd * sizeof(float) > 200 * 1024) HB_REFUSE("attention_talking: %d heads over %d kv heads of %d values need %zu bytes of shared memory", heads, kv_heads, vd, smem);
     const bool vec = vd % 4 == 0 && kd % 4 == 0 && ((uintptr_t)kv % (4 * sizeof(T))) == 0;   // runs of four never cross a kv head
+    {   // rows of one token whose sizes the staged kernel takes
+        const int per16 = 16 / (int)sizeof(T), runs = all / 4;
+        const int ng = runs > 0 && runs <= R1_THREADS && R1_THREADS % runs == 0 ? R1_THREADS / runs : 0;
+        const int hpt = !ng ? 0 : heads % ng == 0 ? heads / ng : heads < ng ? 1 : 0;    // (fewer heads than groups: some threads idle)
+        const size_t bytes = (((size_t)heads * (kd + R1_KEYS + 3) + 3) & ~(size_t)3) * sizeof(float)
+                             + (size_t)kv_heads * R1_KEYS * (kd + vd + per16) * sizeof(T);
+        if (splits > 1 && tokens == rows && vec && (kd + vd) % per16 == 0 && ((uintptr_t)kv % 16) == 0 && bytes <= 200 * 1024
+                && (hpt == 1 || hpt == 2 || hpt == 4 || hpt == 8 || hpt == 16)) {
+#define HB_ROWS1(H) do { \
+                auto kernel = talking_rows1_kernel<T, H>; \
+                if (bytes > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes)); \
+                kernel<<<dim3(tokens, splits), R1_THREADS, bytes, s>>>((const T*)q, (const T*)kv, block_table, table_stride, row_slot, \
+                    kv_len, heads, kv_heads, kd, vd, pages, page_size, scale, head_scale, chunk, window, partial); \
+            } while (0)
+            if (hpt == 1) HB_ROWS1(1); else if (hpt == 2) HB_ROWS1(2); else if (hpt == 4) HB_ROWS1(4);
+            else if (hpt == 8) HB_ROWS1(8); else HB_ROWS1(16);
+#undef HB_ROWS1
+            HB_LAUNCH_CHECK("talking_rows1");
+            return launch_talking_merge<T>(out, partial, splits, tokens, heads, kv_heads, vd, talk, s);
+        }
+    }
 #define HB_TALK(E) do { \
         auto kernel = splits > 1 ? (vec && E >= 4 ? attention_talking_kernel<T, E, true, (E >= 4)> : attention_talking_kernel<T, E, true, false>) \
                                  : (vec && E >= 4 ? attention_talking_kernel<T, E, false, (E >= 4)> : attention_talking_kernel<T, E, false, false>); \
@@ -403,13 +553,7 @@ static int launch_talking(void* out, const void* q, const void* kv, const int32_
     else HB_REFUSE("attention_talking: %d kv heads of %d values are above 1024 numbers a head", kv_heads, vd);
 #undef HB_TALK
     HB_LAUNCH_CHECK("attention_talking");
-    if (splits > 1) {
-        const int slices = vd >= TM_THREADS ? 1 : TM_THREADS / vd;
-        const size_t merge_bytes = ((size_t)2 * heads * splits + (size_t)slices * vd) * sizeof(float);
-        if (merge_bytes > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(talking_merge_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_bytes));
-        talking_merge_kernel<T><<<dim3(tokens, heads), TM_THREADS, merge_bytes, s>>>((T*)out, partial, splits, heads, kv_heads, vd, talk);
-        HB_LAUNCH_CHECK("talking_merge");
-    }
+    if (splits > 1) return launch_talking_merge<T>(out, partial, splits, tokens, heads, kv_heads, vd, talk, s);
     return 0;
 }
 

@@ -229,10 +229,14 @@ def test_talking_attention_rows_of_unequal_requests(K, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("part", [8, 32, 64])
-def test_one_token_rows_with_their_keys_in_parts(K, dtype, part, monkeypatch):
+@pytest.mark.parametrize("heads,kv_heads,kd,vd", [(6, 2, 40, 24), (8, 2, 64, 64), (16, 4, 128, 128), (32, 8, 128, 128),
+                                                  (4, 2, 96, 64), (3, 1, 24, 128), (16, 1, 32, 8)])
+def test_one_token_rows_with_their_keys_in_parts(K, dtype, part, heads, kv_heads, kd, vd, monkeypatch):
     """Rows of one token whose keys are cut into parts of unequal fill (the last part short, some parts empty for the
-    shorter row), merged by the second kernel: maxima, sums and weighted values of the parts, then the heads' mixing."""
-    heads, kv_heads, kd, vd, chunk, page = 6, 2, 40, 24, 150, 16
+    shorter row), merged by the second kernel: maxima, sums and weighted values of the parts, then the heads' mixing.
+    Sizes that the kernel with tiles in shared memory takes (1, 4 and 16 heads a thread, fewer heads than thread
+    groups) and sizes it leaves to the plain one."""
+    chunk, page = 150, 16
     lens, slots = [431, 309, 7], [2, 0, 1]                   # 132, 10 and 7 keys in sight
     scale = 2.0 / kd ** 0.5
     temp, talk = 1.0 + 0.3 * rand(heads, seed=4), torch.eye(heads) + 0.4 * rand(heads, heads, seed=5)
