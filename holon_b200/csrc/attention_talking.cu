@@ -486,7 +486,19 @@ __global__ void talking_mix_kernel(T* __restrict__ out, const T* __restrict__ wi
     const int n = heads * kv_heads * vd;
     const T* src = wide_in + t * n;
     float* mix = tk_smem + n;                                // the mixing matrix beside the token's rows
-    for (int e = threadIdx.x; e < n; e += blockDim.x) tk_smem[e] = to_f32(src[e]);
+    if (sizeof(T) == 2 && (n & 7) == 0 && ((uintptr_t)wide_in & 15) == 0) {      // bfloat16 rows in pieces of 16 bytes
+        for (int e = threadIdx.x; e < (n >> 3); e += blockDim.x) {
+            const uint4 w = ((const uint4*)src)[e];
+            const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                tk_smem[8 * e + 2 * i] = __uint_as_float(u[i] << 16);
+                tk_smem[8 * e + 2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+            }
+        }
+    } else {
+        for (int e = threadIdx.x; e < n; e += blockDim.x) tk_smem[e] = to_f32(src[e]);
+    }
     if (talk) for (int e = threadIdx.x; e < heads * heads; e += blockDim.x) mix[e] = talk[e];
     __syncthreads();
     talking_mix_store<T>(out, tk_smem, talk ? mix : nullptr, t, heads, kv_heads, vd);
