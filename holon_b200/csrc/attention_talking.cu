@@ -15,8 +15,9 @@
 // hb_attention_talking    any sizes on CUDA cores, 32-bit arithmetic: the float32 engine's kernel, and the bfloat16
 //                         engine's for one-token rows and for sizes the tensor-core kernel refuses. With `splits` > 1 a
 //                         token's keys are cut into that many parts, a block each, and a second kernel merges the
-//                         parts (running maxima, sums, weighted values) before the heads are mixed: rows of one token
-//                         then fill the GPU.
+//                         parts (running maxima, sums, weighted values) and mixes the heads: rows of one token then
+//                         fill the GPU. Where every row has one token and the sizes allow, the parts run on a kernel
+//                         that stages the keys and values in shared memory once for all heads (talking_rows1_kernel).
 // hb_talking_mix          the mixing alone, for rows whose per-(query head, kv head) results the tensor-core prompt
 //                         kernel (csrc/attention_tcgen05.cu, value_heads = kv_heads) has left
 #include "common.cuh"

@@ -48,7 +48,8 @@ __global__ void mlstm_gates_kernel(float* __restrict__ out, const float* __restr
         __syncthreads();
         if (threadIdx.x == 0) {
             float mx = sm[0];
-            for (int j = 0; j < m; ++j) { mx = fmaxf(sf[j] + mx, si[j]); sm[j + 1] = mx; }
+#pragma unroll 8
+            for (int j = 0; j < m; ++j) { mx = fmaxf(sf[j] + mx, si[j]); sm[j + 1] = mx; }    // (loads run ahead of the chain)
         }
         __syncthreads();
         for (int j = threadIdx.x; j < m; j += blockDim.x) {

@@ -1186,7 +1186,7 @@ class CudaKernels:
         splits, partial = 1, None
         if n_rows == rows.n_decode and n_rows:                        # rows of one token only: their keys in parts
             keys = min(x for x in (rows.max_kv, chunk, window) if x > 0)
-            splits = max(1, min(-(-2 * self.sms // n_tokens), -(-keys // self.TALKING_SPLIT_KEYS), 64))
+            splits = max(1, min(-(-self.sms // n_tokens), -(-keys // self.TALKING_SPLIT_KEYS), 64))   # about a block an SM
             if splits > 1:
                 partial = torch.empty(n_tokens * splits * heads * (kv_heads * vd + 2), dtype=torch.float32, device=q.device)
         self._call("hb_attention_talking", self._p(out), self._p(q), self._p(kv), _code(q), *common, n_rows, n_tokens, heads,

@@ -230,7 +230,7 @@ def test_talking_attention_rows_of_unequal_requests(K, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("part", [8, 32, 64])
 @pytest.mark.parametrize("heads,kv_heads,kd,vd", [(6, 2, 40, 24), (8, 2, 64, 64), (16, 4, 128, 128), (32, 8, 128, 128),
-                                                  (4, 2, 96, 64), (3, 1, 24, 128), (16, 1, 32, 8)])
+                                                  (4, 2, 72, 48), (3, 1, 24, 128), (16, 1, 32, 8)])
 def test_one_token_rows_with_their_keys_in_parts(K, dtype, part, heads, kv_heads, kd, vd, monkeypatch):
     """Rows of one token whose keys are cut into parts of unequal fill (the last part short, some parts empty for the
     shorter row), merged by the second kernel: maxima, sums and weighted values of the parts, then the heads' mixing.
@@ -346,7 +346,7 @@ def _memory_step(kernels, dev, first, pre, bias, gain, cap, eps, heads, dim, vdi
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,dim,vdim,cap", [(2, 8, 12, 12.0), (1, 12, 20, 3.0), (2, 96, 40, 8.0), (3, 16, 8, 5.0),
-                                               (2, 128, 256, 15.0), (1, 4, 4, 5.0), (2, 32, 64, 12.0)])
+                                               (2, 128, 256, 15.0), (1, 4, 4, 5.0), (4, 32, 48, 11.0)])
 def test_memory_rows_in_slots_and_in_portions(K, dtype, heads, dim, vdim, cap):
     """Rows of 1, 1, 2, 11 and 37 tokens in slots of their own, twice: the second call goes on from the state, the
     normaliser and the running maximum that the first left. The gates' pre-activations spread over ± 3 caps, so the cap
