@@ -1,2 +1,2 @@
 """Built-in architectures; importing this package registers them."""
-from . import kasovik, qwen3, rulorax, tilarax  # noqa: F401
+from . import kasovik, qwen3, rulorax, tilarax, vobosun  # noqa: F401

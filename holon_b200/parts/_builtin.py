@@ -1,16 +1,16 @@
 """Registers the parts that ship with the framework."""
 from .attention import GQA, TalkingAttention
 from .base import register_part
-from .block import OutNorm, PreNorm
+from .block import OutNorm, PreNorm, Sandwich
 from .embedding import Embedding, Head, PairEmbedding
 from .experts import Experts
 from .feedforward import MLP, ClampedGLU, SwiGLU
 from .hyper import Hyper
 from .latent import LatentAttention
-from .norm import RMSNorm
+from .norm import DynamicTanh, RMSNorm
 from .parallel import ParallelBlock, SideBySide
 from .position import Rope
-from .recurrent import MLSTM, GatedDelta, Retention
+from .recurrent import MLSTM, GatedDelta, GeneralDelta, Retention
 
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
 register_part("position", "rope", Rope, replace=True)
@@ -32,3 +32,6 @@ register_part("mixer", "talking", TalkingAttention, replace=True)
 register_part("mixer", "mlstm", MLSTM, replace=True)
 register_part("ffn", "mlp", MLP, replace=True)
 register_part("block", "outnorm", OutNorm, replace=True)
+register_part("norm", "dyt", DynamicTanh, replace=True)
+register_part("block", "sandwich", Sandwich, replace=True)
+register_part("mixer", "general_delta", GeneralDelta, replace=True)

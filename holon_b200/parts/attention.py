@@ -12,7 +12,8 @@ Options that other designs use, each a constructor argument: `scale` (the score 
 the merged product then has the key's rows twice, so that the cache write stores the normed copy as the key and the
 plain copy as the value); `sink` (one learned number per head, stored as `sink`: exp(sink) stands in the softmax's
 denominator, without key or value and without the score scale); `names` (the stored names of the q, k, v and output
-weights, where they are not `q_proj.weight` and so on).
+weights, where they are not `q_proj.weight` and so on); `biases` (q, k and v carry biases, stored under the weights'
+names with `.b` behind the stem, added before norm and rotation; the output projection has none).
 """
 from __future__ import annotations
 
@@ -27,8 +28,10 @@ class GQA(Part):
     def __init__(self, ctx: BuildContext, *, heads: int, kv_heads: int, head_dim: int, hidden: int,
                  position: PartRef | None, qk_norm: PartRef | None = None, window: int = 0, layer: int = 0,
                  scale: float | None = None, unit_norm_eps: float | None = None, values_are_keys: bool = False,
-                 sink: bool = False, names: tuple[tuple[str, str], ...] = ()) -> None:
+                 sink: bool = False, names: tuple[tuple[str, str], ...] = (), biases: bool = False) -> None:
         super().__init__()
+        if biases and values_are_keys:
+            raise ValueError("gqa: biases do not go with values_are_keys")
         if heads % kv_heads:
             raise ValueError(f"gqa: {heads} heads are no multiple of {kv_heads} kv heads")
         if qk_norm is not None and unit_norm_eps is not None:
@@ -45,6 +48,14 @@ class GQA(Part):
                                                 spare=kv_heads * head_dim if values_are_keys else 0))
         self.o_proj = self.add_child("o_proj", Linear(ctx, "weight", heads * head_dim, {"weight": hidden}))
         self.sink = self.add_param("sink", (heads,), "coef") if sink else None
+        self.bias = None
+        if biases:                           # one vector beside the merged product's rows: q | k | v
+            nq, nk = heads * head_dim, kv_heads * head_dim
+            def stem(which):                 # `x.weight` goes with `x.bias`, a bare stored name `x` with `x.b`
+                name = self._names[which]
+                return name[:-len(".weight")] + ".bias" if name.endswith(".weight") else name + ".b"
+            self.bias = self.add_param("qkv_bias", (nq + 2 * nk,), "matrix", {
+                stem("q_proj.weight"): (0, nq), stem("k_proj.weight"): (nq, nq + nk), stem("v_proj.weight"): (nq + nk, nq + 2 * nk)})
         self._unit = None                    # the gain of a norm without a weight: ones (made in finalize)
         self.q_norm = self.k_norm = None
         if qk_norm is not None:
@@ -97,7 +108,9 @@ class GQA(Part):
                  cache.kv if cache.fills else None, cache.group.write_index if cache.fills else None,
                  self.heads, self.kv_heads, self.head_dim)
         fused = getattr(k, "qkv_rope", None)                         # a kernel table may do the product and what follows in one
-        if fused is None or not fused(q, x, self.qkv.weight.tensor, *after):
+        if self.bias is not None:                                    # (the fused product knows no bias)
+            k.qk_norm_rope_kv_write(q, self.qkv.forward(x), *after, bias=self.bias.tensor)
+        elif fused is None or not fused(q, x, self.qkv.weight.tensor, *after):
             k.qk_norm_rope_kv_write(q, self.qkv.forward(x), *after)
         o = self.ctx.empty(t, self.heads, self.head_dim)
         if self.sink is not None:
@@ -116,7 +129,7 @@ class TalkingAttention(Part):
     `talk` [heads, heads] mixes the heads' weights after the softmax (`talking`), `temp` [heads] is a learned factor on each
     head's scores (`head_temperature`); without them the mixer is plain attention. Which keys j ≤ i a query sees: with
     `chunk` C only those of its own block of C positions (blocks counted from the sequence's first token, wherever a
-    prompt was cut), with `window` W only the last W. q and k carry biases (`biases`: q.b, k.b, v.b, o.b) and a per-head
+    prompt was cut), with `window` W only the last W. q and k carry biases (`biases`: q.b, k.b, v.b, o.b; "qkv": none on the output) and a per-head
     RMS norm with one plain weight shared by the heads (`qk_eps` not None: q.norm, k.norm), then the position's
     rotation. `blend`: "keep" leaves this layer's values (as projected, 32-bit) on the step under `blend_key` for later
     layers; "mix" replaces this layer's values by (1 − λ) v + λ v_kept with the stored number `vmix`, and that is what the
@@ -128,7 +141,7 @@ class TalkingAttention(Part):
 
     def __init__(self, ctx: BuildContext, *, heads: int, kv_heads: int, key_dim: int, value_dim: int, hidden: int,
                  scale: float, position: PartRef | None = None, qk_eps: float | None = None, chunk: int = 0,
-                 window: int = 0, talking: bool = True, head_temperature: bool = True, biases: bool = True,
+                 window: int = 0, talking: bool = True, head_temperature: bool = True, biases: bool | str = True,
                  blend: str | None = None, blend_key: str = "values", layer: int = 0) -> None:
         super().__init__()
         if heads % kv_heads:
@@ -142,10 +155,13 @@ class TalkingAttention(Part):
         self.first = self.add_child("first", Linear(ctx, "weight", hidden, {"q": nq, "k": nk, "v": nv}))
         self.out = self.add_child("out", Linear(ctx, "weight", heads * value_dim, {"o": hidden}))
         self.first_bias = self.out_bias = None
+        if biases not in (True, False, "qkv"):
+            raise ValueError(f"talking attention: biases {biases!r}; known: True, False, 'qkv' (none on the output)")
         if biases:
             self.first_bias = self.add_param("first_bias", (nq + nk + nv,), "matrix",
                                              {"q.b": (0, nq), "k.b": (nq, nq + nk), "v.b": (nq + nk, nq + nk + nv)})
-            self.out_bias = self.add_param("o.b", (hidden,), "matrix")
+            if biases is True:
+                self.out_bias = self.add_param("o.b", (hidden,), "matrix")
         self.q_gain = self.add_param("q.norm", (key_dim,), "coef") if qk_eps is not None else None
         self.k_gain = self.add_param("k.norm", (key_dim,), "coef") if qk_eps is not None else None
         self.talk = self.add_param("talk", (heads, heads), "coef") if talking else None

@@ -178,10 +178,11 @@ class Residual:
     added its output itself and left the next norm's rows behind (`normed`, made with the weight of `normed_by`):
     then that norm has nothing left to launch."""
 
-    __slots__ = ("h", "delta", "normed", "normed_by")
+    __slots__ = ("h", "delta", "delta_by", "normed", "normed_by")
 
     def __init__(self, h: torch.Tensor, delta: torch.Tensor | None = None) -> None:
         self.h, self.delta = h, delta
+        self.delta_by = None                 # a norm that `delta` passes before it is added (None: added as it is)
         self.normed, self.normed_by = None, None
 
     def final_rows(self, norm, index: torch.Tensor) -> torch.Tensor:

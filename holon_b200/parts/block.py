@@ -7,13 +7,19 @@ OutNorm: the norm stands on a sublayer's OUTPUT, and the sublayers read the stre
 x ← x + N(ffn(x)). With `average` = n the block ends with an average over depth: with X_0 the embedding's rows and X_j
 what the j-th block before left (before ITS averaging), what goes on is Σ_j c[j] X_j over the n results so far, c the
 block's stored `depth` coefficients. The results of a step's blocks wait on the step (`step.shared`), 32-bit.
+
+Sandwich: a norm before and behind each sublayer, x ← x + N1b(mixer(N1(x))), then x ← x + N2b(ffn(N2(x))). With `shift`
+the mixer reads each token's normed row blended with the row of the token before, m_t = n_t + (n_(t−1) − n_t) · mix with a
+stored vector `shift` (zeros before a sequence's first token); the last normed row of a request's step is kept per
+request and cache entry (a `SlotState` the block declares, `block.shift`). The feed-forward's output stays pending on the
+stream together with its norm, and the next block's first kernel (or the model's last norm) adds it.
 """
 from __future__ import annotations
 
 import torch
 
 from ..config.spec import PartRef
-from .base import BuildContext, Link, Part, Residual
+from .base import BuildContext, Link, Part, Residual, SlotState
 
 
 class PreNorm(Part):
@@ -118,4 +124,41 @@ class OutNorm(Part):
         else:
             k.out_norm_add(own, src, y, bias, norm.weight.tensor, norm.eps, norm.offset, cast=cast)
         state["x"] = cast if cast is not None else stream.h
+        return stream
+
+
+class Sandwich(Part):
+    """Its norms offer `add`, `add_shifted`, `add_then` and `gather` (parts/norm.py: DynamicTanh)."""
+
+    def __init__(self, ctx: BuildContext, *, layer: int, hidden: int, mixer: PartRef, ffn: PartRef | None, norm: PartRef,
+                 shift: bool = False) -> None:
+        super().__init__()
+        self.ctx, self.hidden = ctx, hidden
+        self.mixer_norm = self.add_child("mixer_norm", ctx.part(norm, dim=hidden))
+        self.mixer = self.add_child("mixer", ctx.part(mixer, layer=layer, hidden=hidden))
+        self.mixer_out_norm = self.add_child("mixer_out_norm", ctx.part(norm, dim=hidden))
+        self.ffn_norm = self.ffn = self.ffn_out_norm = None
+        if ffn is not None:
+            self.ffn_norm = self.add_child("ffn_norm", ctx.part(norm, dim=hidden))
+            self.ffn = self.add_child("ffn", ctx.part(ffn, layer=layer, hidden=hidden))
+            self.ffn_out_norm = self.add_child("ffn_out_norm", ctx.part(norm, dim=hidden))
+        self.shift = self.add_param("shift", (hidden,), "coef") if shift else None
+
+    def slot_states(self):
+        """What the block itself carries per request and cache entry (the model files it beside the mixer's)."""
+        return (SlotState("block.shift", (self.hidden,)),) if self.shift is not None else ()
+
+    def forward(self, stream: Residual, step, cache, after=None) -> Residual:
+        stream.normed = stream.normed_by = None
+        if self.shift is not None:
+            x = self.mixer_norm.add_shifted(stream, self.shift.tensor, cache.slots["block.shift"], step.rows)
+        else:
+            x = self.mixer_norm.add(stream)
+        step.link = None
+        y = self.mixer.forward(x, step, cache)
+        if self.ffn is None:
+            stream.delta, stream.delta_by = y, self.mixer_out_norm
+            return stream
+        x = self.mixer_out_norm.add_then(stream, y, self.ffn_norm)
+        stream.delta, stream.delta_by = self.ffn.forward(x, step), self.ffn_out_norm
         return stream

@@ -5,7 +5,8 @@ ClampedGLU: a gated unit whose inputs are clamped, with a bias on every projecti
 u = clamp(W_up x + b, −limit, limit), y = g · sigmoid(alpha · g) · (u + 1), output W_down y + b.
 
 MLP: W_down act(W_up x), no gate and no bias; `activation` as the experts name theirs ("gelu_tanh": the tanh form of
-gelu, 0.5 z (1 + tanh(√(2/π) (z + 0.044715 z³))))."""
+gelu, 0.5 z (1 + tanh(√(2/π) (z + 0.044715 z³))); "xielu": with two stored numbers p, q (`act`), softplus(p) z² + z/2 for
+z > 0 and (1/2 + softplus(q)) (exp(z) − 1 − z) + z/2 otherwise)."""
 from __future__ import annotations
 
 import torch
@@ -71,6 +72,7 @@ class MLP(Part):
         if activation not in ACTIVATIONS:
             raise ValueError(f"mlp: activation {activation!r}; known: {sorted(ACTIVATIONS)}")
         self.ctx, self.inter, self.act = ctx, inter, ACTIVATIONS[activation]
+        self.numbers = self.add_param("act", (2,), "coef") if activation == "xielu" else None
         self.up = self.add_child("up_proj", Linear(ctx, "weight", hidden, {"up": inter}))
         self.down = self.add_child("down_proj", Linear(ctx, "weight", inter, {"down": hidden}))
 
@@ -83,5 +85,8 @@ class MLP(Part):
 
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         z = self.up.forward(x)
-        self.ctx.kernels.activation(z, self.act)
+        if self.numbers is not None:
+            self.ctx.kernels.activation(z, self.act, self.numbers.tensor)
+        else:
+            self.ctx.kernels.activation(z, self.act)
         return self.down.forward(z)

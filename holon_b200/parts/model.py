@@ -64,8 +64,11 @@ class Model(Part):
         if carried:                                           # what the embedding carries from step to step per request
             entries[EMBED_ENTRY] = CacheEntry(EMBED_ENTRY, -1, None, carried)
         for run in self.spec.order:
-            mixer = self.layers[run.layer].mixer
+            block = self.layers[run.layer]
+            mixer = block.mixer
             decl, slots = mixer.cache(), tuple(mixer.slot_states())
+            if hasattr(block, "slot_states"):                 # what the block itself carries per request (names `block.*`)
+                slots += tuple(block.slot_states())
             if run.fills:
                 entries[run.cache] = CacheEntry(run.cache, run.layer, decl, slots)
             elif entries[run.cache].decl != decl:

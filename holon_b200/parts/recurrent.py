@@ -22,6 +22,16 @@ dim^(−1/2); each head's o divided by its root mean square, times a weight over
 then W_o. n rides as one more value column of S (the value row gets a 1 behind it), so the update is the same scan with a
 decay per head and token; m is a second `SlotState`. The gates' projections leave their product in 32-bit.
 
+`GeneralDelta`: the generalized delta rule. Per head, with r, k, v of one size `dim`, a decay w per key channel and token
+and a removal rate a per key channel and token, and the token's unit key u = k / sqrt(Σk² + unit_eps):
+
+    S ← diag(w) S − (a ∘ u)(uᵀ S) + k vᵀ   (both terms read the old S),   o = Sᵀ r;
+
+w = exp(−decay_scale · sigmoid(W_w2 tanh(W_w1 x) + w0)) through a low-rank pair, a = sigmoid(W_a x + b_a). Since u is k
+times one number c per head and token, the removal term is k_i · a_i c² · (kᵀ S)_j: the scan takes the rate a c² per key
+channel beside k itself (`recurrent_scan(rate=)`). Each head's o is divided by its root mean square, times a weight over
+all heads' channels, times sigmoid(W_g x), then W_o.
+
 Everything that enters the recurrence is 32-bit (the scan's inputs are made in 32-bit from the first product's rows);
 the products themselves are the engine's. All first projections of a mixer are one merged product.
 """
@@ -33,6 +43,8 @@ from ..config.spec import PartRef
 from .base import BuildContext, Part, SlotState
 from .linear import Linear
 
+ACT_TANH = 5                          # the kernel table's activation code (parts/experts.py: ACTIVATIONS)
+
 
 class _MatrixState(Part):
     """What both mixers share: no paged cache, one state matrix per head, loadable names without the children's."""
@@ -41,7 +53,7 @@ class _MatrixState(Part):
         return None
 
     def _strip(self, prefix: str, name: str) -> str:
-        for child in ("first.", "low.", "out.", "gates."):
+        for child in ("first.", "low.", "high.", "out.", "gates."):
             if name.startswith(prefix + child):
                 return prefix + name[len(prefix + child):]
         return name
@@ -186,3 +198,41 @@ class MLSTM(_MatrixState):
         at = 2 * heads * dim + heads * vdim
         k.mlstm_read_out(y, o1, gates[2], self.gain.tensor, first[:, at:at + heads * vdim], self.eps, self.TINY)
         return self.out.forward(y.view(t, heads * vdim))
+
+
+class GeneralDelta(_MatrixState):
+    def __init__(self, ctx: BuildContext, *, heads: int, dim: int, decay_rank: int, eps: float, hidden: int,
+                 decay_scale: float = 0.6065306597126334, unit_eps: float = 1e-6, layer: int = 0) -> None:
+        super().__init__()
+        if min(heads, dim, decay_rank) < 1:
+            raise ValueError("general delta: heads, dim and decay_rank must be positive")
+        self.ctx, self.heads, self.dim, self.eps = ctx, heads, dim, float(eps)
+        self.decay_scale, self.unit_eps = float(decay_scale), float(unit_eps)
+        n = heads * dim
+        self.first = self.add_child("first", Linear(ctx, "weight", hidden, {"r": n, "k": n, "v": n, "g": n, "a": n}))
+        self.low = self.add_child("low", Linear(ctx, "weight", hidden, {"w1": decay_rank}))
+        self.high = self.add_child("high", Linear(ctx, "weight", decay_rank, {"w2": n}))
+        self.decay_bias = self.add_param("w0", (n,), "coef")
+        self.rate_bias = self.add_param("a.b", (n,), "coef")
+        self.gain = self.add_param("norm", (n,), "coef")
+        self.out = self.add_child("out", Linear(ctx, "weight", n, {"o": hidden}))
+
+    def slot_states(self):
+        return (SlotState("state", (self.heads, self.dim, self.dim)),)
+
+    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+        t, k, ctx, heads, dim = x.shape[0], self.ctx.kernels, self.ctx, self.heads, self.dim
+        f32, n = torch.float32, heads * dim
+        first = self.first.forward(x)                                    # [t, r | k | v | g | a]
+        low = self.low.forward(x)
+        k.activation(low, ACT_TANH)
+        pre = self.high.forward(low, out_dtype=f32)                      # [t, heads dim]: the decays before bias and sigmoid
+        qk, v = ctx.empty(t, 2, heads, dim, dtype=f32), ctx.empty(t, heads, dim, dtype=f32)
+        decay, rate = ctx.empty(t, heads, dim, dtype=f32), ctx.empty(t, heads, dim, dtype=f32)
+        k.gdelta_prepare(qk, v, decay, rate, first, pre, self.decay_bias.tensor, self.rate_bias.tensor,
+                         self.decay_scale, self.unit_eps)
+        o = ctx.empty(t, heads, dim, dtype=f32)
+        k.recurrent_scan(o, qk, v, decay, None, None, cache.slots["state"], step.rows, rate=rate)
+        y = ctx.empty(t, heads, dim)
+        k.head_norm_gate(y, o, self.gain.tensor, None, first[:, 3 * n:4 * n], self.eps, gate="sigmoid")
+        return self.out.forward(y.view(t, n))

@@ -40,8 +40,10 @@ class RefKernels:
         self.rmsnorm(out, v, weight, eps, offset)
 
     def qk_norm_rope_kv_write(self, q_out, qkv, positions, table, rotary_dim, q_weight, k_weight, eps, offset, kv,
-                              write_index, heads, kv_heads, head_dim):
+                              write_index, heads, kv_heads, head_dim, bias=None):
         t, dt = qkv.shape[0], qkv.dtype
+        if bias is not None:
+            qkv = (qkv.float() + bias.float()).to(dt)
         q, k, v = qkv.split([heads * head_dim, kv_heads * head_dim, kv_heads * head_dim], dim=-1)
         q, k, v = q.reshape(t, heads, head_dim), k.reshape(t, kv_heads, head_dim), v.reshape(t, kv_heads, head_dim)
 
@@ -134,7 +136,7 @@ class RefKernels:
         g, u = g.clamp(max=limit), u.clamp(-limit, limit)
         out.copy_((g * torch.sigmoid(alpha * g) * (u + 1)).to(out.dtype))
 
-    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows, token_decay=None):
+    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows, token_decay=None, rate=None):
         t, heads, vdim = v.shape
         group = heads // qk.shape[2]
         qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
@@ -143,6 +145,10 @@ class RefKernels:
                 s = state[slots[b], h].T.clone()               # (kept column by column: [vdim, dim])
                 for i in range(qs[b], qs[b + 1]):
                     q, k = qk[i, 0, h // group], qk[i, 1, h // group]
+                    if rate is not None:                       # the generalized rule: the removal reads the old state
+                        s = s * decay[i, h][:, None] + torch.outer(k, v[i, h]) - torch.outer(rate[i, h] * k, s.T @ k)
+                        out[i, h] = s.T @ q
+                        continue
                     s = s * (decay[i, h][:, None] if decay is not None else
                              token_decay[i, h] if token_decay is not None else head_decay[h])
                     u = v[i, h] if beta is None else beta[i, h] * (v[i, h] - s.T @ k)
@@ -194,15 +200,15 @@ class RefKernels:
             qk[:, which] = z * (k_scale if which else 1.0)
         v.copy_(x[:, 2 * heads * dim:2 * heads * dim + heads * vdim].view(t, heads, vdim))
 
-    def head_norm_gate(self, out, o, weight, gate_mul, gate_pre, eps):
+    def head_norm_gate(self, out, o, weight, gate_mul, gate_pre, eps, gate="silu"):
         y = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps)
-        if weight is not None:
-            y = y * weight
+        if weight is not None:                                 # one weight for all heads, or one per head and channel
+            y = y * (weight.view(o.shape[1:]) if weight.numel() == o.shape[1] * o.shape[2] else weight)
         if gate_mul is not None:
             y = y * gate_mul.view(o.shape)
         elif gate_pre is not None:
-            g = gate_pre.float().view(o.shape)
-            y = y * g * torch.sigmoid(g)
+            g = gate_pre.float().reshape(o.shape)
+            y = y * (g * torch.sigmoid(g) if gate == "silu" else torch.sigmoid(g))
         out.copy_(y.to(out.dtype))
 
     def feed_tokens(self, token_ids, last_tokens, rows, from_last):
@@ -321,21 +327,29 @@ class RefKernels:
     def sigmoid_gate(self, o, g):
         o.copy_((o.float() * torch.sigmoid(g.float())).to(o.dtype))
 
-    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize, bias=None):
+    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize, bias=None, correction=None, groups=1,
+                  keep=1, tiny=0.0):
         z = z[:, :experts].float() + (bias.float() if bias is not None else 0.0)
         s = torch.softmax(z, dim=-1)
         top = chosen.shape[1]
-        order = torch.argsort(-s, dim=-1, stable=True)[:, :top]           # equal scores: the lower expert first
+        choice = s + correction.float() if correction is not None else s.clone()
+        if groups > 1:                                         # only experts of the best groups stay in the running
+            best = choice.view(-1, groups, experts // groups).max(-1).values
+            kept = torch.argsort(-best, dim=-1, stable=True)[:, :keep]
+            allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
+            choice = choice.masked_fill(~allowed.repeat_interleave(experts // groups, dim=1), float("-inf"))
+        order = torch.argsort(-choice, dim=-1, stable=True)[:, :top]      # equal scores: the lower expert first
         w = torch.gather(s, 1, order)
         if renormalize:
-            w = w / w.sum(-1, keepdim=True)
+            w = w / (w.sum(-1, keepdim=True) + tiny)
         chosen.copy_(order.to(torch.int32))
         weight.copy_(w * scale)
         counts[:experts] += torch.bincount(order.reshape(-1), minlength=experts).to(torch.int32)
 
-    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize, bias=None):
+    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize, bias=None,
+                   correction=None, groups=1, keep=1, tiny=0.0):
         counts.zero_()
-        self.route_top(chosen, weight, counts, z, experts, scale, renormalize, bias)
+        self.route_top(chosen, weight, counts, z, experts, scale, renormalize, bias, correction, groups, keep, tiny)
         self.expert_rows(place, token_of, counts, chosen, experts)
         counts[2 * experts + 1], counts[2 * experts + 2] = 0, chosen.shape[0]
 
@@ -350,7 +364,13 @@ class RefKernels:
         token_of.copy_((order // top).to(torch.int32))
 
     @staticmethod
-    def _act(x, act):
+    def _act(x, act, numbers=None):
+        if act == 4:                                           # xielu with its two stored numbers
+            sp = torch.nn.functional.softplus
+            p, q = numbers.float()
+            return torch.where(x > 0, sp(p) * x * x + 0.5 * x, (0.5 + sp(q)) * (torch.expm1(x) - x) + 0.5 * x)
+        if act == 5:
+            return torch.tanh(x)
         if act == 1:
             return torch.relu(x) ** 2
         if act == 2:
@@ -367,16 +387,20 @@ class RefKernels:
                 rows = x[token_of[a:b].long()] if token_of is not None else x[a:b]
                 out[a:b] = self._act(rows.float() @ w[e].float().T, act).to(out.dtype)
 
-    def activation(self, x, act):
-        x.copy_(self._act(x.float(), act).to(x.dtype))
+    def activation(self, x, act, numbers=None):
+        x.copy_(self._act(x.float(), act, numbers).to(x.dtype))
 
-    def expert_combine(self, out, y, place, weight, shared, z, experts):
+    def expert_combine(self, out, y, place, weight, shared, z, experts, x=None, identity_from=None):
         t, top = weight.shape
         acc = torch.zeros(out.shape, dtype=torch.float32)
         for k in range(top):
-            acc += weight[:, k:k + 1] * y[place.view(t, top)[:, k].long()].float()
+            rows = place.view(t, top)[:, k].long()
+            term = y[rows].float()
+            if x is not None:                                  # rows of identity experts: the token's input itself
+                term = torch.where((rows >= int(identity_from[0]))[:, None], x.float(), term)
+            acc += weight[:, k:k + 1] * term
         if shared is not None:
-            acc += torch.sigmoid(z[:, experts:experts + 1].float()) * shared.float()
+            acc += (torch.sigmoid(z[:, experts:experts + 1].float()) if z is not None else 1.0) * shared.float()
         out.copy_(acc.to(out.dtype))
 
     # ---- the matrix memory with exponential gates
@@ -492,3 +516,45 @@ class RefKernels:
                     probs = talk.float() @ probs
                 for h in range(heads):
                     out[i, h] = (probs[h] @ values[h // group, lo:pos + 1]).to(out.dtype)
+
+    # ---- a norm without statistics, a token's rows blended with the token before's, the generalized delta rule
+    @staticmethod
+    def _dyt(x, triple):
+        alpha, w, b = triple
+        return torch.tanh(alpha.float() * x.float()) * w.float() + b.float()
+
+    def dyt_add_norm(self, h, y, post, out, pre, index):
+        """h += N_post(y) (y None: nothing is added; `h` None: `y` itself is the input of N_pre); out = N_pre(rows)."""
+        if h is None:
+            out.copy_(self._dyt(y, pre).to(out.dtype))
+            return
+        rows = slice(None) if index is None else index.long()
+        v = h[rows] if y is None else h[rows] + self._dyt(y[rows], post)
+        if index is None and y is not None:
+            h.copy_(v)
+        if out is not None:
+            out.copy_(self._dyt(v, pre).to(out.dtype))
+
+    def dyt_shift(self, out, into, h, y, post, pre, mix, carried, rows):
+        v = h if y is None else h + self._dyt(y, post)
+        n = self._dyt(v, pre)
+        qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
+        for b in range(rows.n_rows):
+            s, e = qs[b], qs[b + 1]
+            if e == s:
+                continue
+            before = torch.cat((carried[slots[b]][None].float(), n[s:e - 1]), 0)
+            out[s:e] = (n[s:e] + (before - n[s:e]) * mix.float()).to(out.dtype)
+            carried[slots[b]] = n[e - 1]
+        into.copy_(v)
+
+    def gdelta_prepare(self, qk, v, decay, rate, first, pre, decay_bias, rate_bias, decay_scale, unit_eps):
+        t, heads, dim = v.shape
+        n = heads * dim
+        x = first.float()
+        r, k = x[:, :n].view(t, heads, dim), x[:, n:2 * n].view(t, heads, dim)
+        qk[:, 0], qk[:, 1] = r, k
+        v.copy_(x[:, 2 * n:3 * n].view(t, heads, dim))
+        decay.copy_(torch.exp(-decay_scale * torch.sigmoid(pre.float() + decay_bias)).view(t, heads, dim))
+        a = torch.sigmoid(x[:, 4 * n:5 * n] + rate_bias).view(t, heads, dim)
+        rate.copy_(a / ((k * k).sum(-1, keepdim=True) + unit_eps))
