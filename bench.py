@@ -139,6 +139,34 @@ TILARAX_SIZES = {
 }
 
 
+def vobosun_config(width: int, heads: int, kv_heads: int, dim: int, ff: int, experts: int, identity: int, top: int,
+                   groups: int, keep: int, expert_ff: int, shared_ff: int, delta_heads: int, delta_dim: int, rank: int,
+                   layers: int, vocab: int = 32768) -> dict:
+    """A Vobosun model for `--only vobosun`: of every three layers the first is a generalized delta rule layer, the others
+    attention with biases and a stretched rotation; odd layers have routed gated experts in groups (with identity experts
+    and a shared one), even layers a dense xielu feed-forward; every layer blends its mixer's input with the token before."""
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                 "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 2.0}}}
+    delta = {"heads": delta_heads, "dim": delta_dim, "decay_rank": rank}
+    moe = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}},
+           "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
+    return {"architecture": "Vobosun", "width": width, "vocab": vocab, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention" if i % 3 else "general_delta", "mixer": attention if i % 3 else delta,
+                        "mlp": moe if i % 2 else {"kind": "dense", "ff": ff}} for i in range(layers)]}
+
+
+# Layers of the sizes of published decoders of 1.5 and 8 billion parameters (as Kasovik's): delta-rule heads of 128 x 128,
+# 28 experts and 4 identity experts in 8 groups of which 4 are kept, 4 chosen, whose sizes together are the dense
+# feed-forward's. Beside each the Kasovik model of `KASOVIK_SIZES` (attention beside a delta rule over a matrix state: the
+# closest design here) and the Qwen3 decoder of the same width, heads, key heads and layers.
+VOBOSUN_SIZES = {
+    "base": (dict(width=2048, heads=16, kv_heads=4, dim=128, ff=6144, experts=28, identity=4, top=4, groups=8, keep=4,
+                  expert_ff=1536, shared_ff=1536, delta_heads=16, delta_dim=128, rank=64, layers=6), "base"),
+    "wide": (dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, experts=28, identity=4, top=4, groups=8, keep=4,
+                  expert_ff=3072, shared_ff=3072, delta_heads=32, delta_dim=128, rank=128, layers=6), "wide"),
+}
+
+
 def _find_number(data, key: str):
     """The first number stored under `key` anywhere in a nested JSON value (a dict under the key: its "value")."""
     if isinstance(data, dict):
@@ -603,6 +631,13 @@ def tilarax_run(args) -> dict:
     return beside_qwen3(args, "tilarax", table, tilarax_config, args.tilarax_sizes, context=1536)
 
 
+def vobosun_run(args) -> dict:
+    """The same for Vobosun beside the Kasovik model and the Qwen3 decoder of the same width, heads, key heads and layers."""
+    table = {name: (ours, KASOVIK_SIZES[like][1], {"kasovik": kasovik_config(**KASOVIK_SIZES[like][0])})
+             for name, (ours, like) in VOBOSUN_SIZES.items()}
+    return beside_qwen3(args, "vobosun", table, vobosun_config, args.vobosun_sizes)
+
+
 def beside_qwen3(args, design: str, table: dict, make_config, chosen: str, context: int = 2048) -> dict:
     import gc
     import torch
@@ -751,6 +786,8 @@ def run_ours(args) -> dict:
         return kasovik_run(args)
     if args.only == "tilarax":
         return tilarax_run(args)
+    if args.only == "vobosun":
+        return vobosun_run(args)
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -873,7 +910,7 @@ def main() -> int:
                          "several passes should hold a few GB only (e.g. 0.03 with --layers 4 --batch 8)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt", "rulorax", "kasovik", "tilarax"),
+    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt", "rulorax", "kasovik", "tilarax", "vobosun"),
                     help="run one part only (for profiling a small case); the JSON line then lacks the other parts. "
                          "long_prompt: time to first token of a 30,000-token prompt behind three decoding requests; "
                          "sizes: the workloads of the Qwen3-32B and Qwen3-0.6B configurations (--sizes); "
@@ -883,6 +920,7 @@ def main() -> int:
     ap.add_argument("--rulorax-sizes", default="", help="with --only rulorax: which sizes (lite, small; default both)")
     ap.add_argument("--kasovik-sizes", default="", help="with --only kasovik: which sizes (base, wide; default both)")
     ap.add_argument("--tilarax-sizes", default="", help="with --only tilarax: which sizes (base, wide; default both)")
+    ap.add_argument("--vobosun-sizes", default="", help="with --only vobosun: which sizes (base, wide; default both)")
     ap.add_argument("--no-points", action="store_true", help="leave out the points at other batch sizes and contexts")
     ap.add_argument("--no-kernels", action="store_true", help="leave out the per-kernel table")
     args = ap.parse_args()

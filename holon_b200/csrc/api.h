@@ -37,12 +37,13 @@ int hb_silu_mul(void* out, const void* gate_up, int dtype, int tokens, int inter
 // Per token and head: RMSNorm over the head (if weights are given), rounding, rotation of the first rotary_dim
 // dimensions in half-split pairs with cos|sin rows of `table` [max_positions, rotary_dim], rounding. q goes to q_out
 // [tokens, heads, head_dim]; k and v go to kv [pages, 2, kv_heads, page_size, head_dim] at write_index = page *
-// page_size + offset (a negative or out-of-range index skips the token). kv may be null (q only).
+// page_size + offset (a negative or out-of-range index skips the token). kv may be null (q only). `bias` (or null): one
+// vector [(heads + 2 kv_heads) head_dim] of `dtype` that is added to q, k and v first.
 int hb_qk_norm_rope_kv_write(void* q_out, const void* qkv, int dtype, const int32_t* positions, const float* table,
                              int rotary_dim, int max_positions, const void* q_weight, const void* k_weight,
                              int weight_dtype, float eps, float offset, void* kv, const int32_t* write_index,
                              int pages, int page_size, int tokens, int heads, int kv_heads, int head_dim,
-                             hb_stream stream);
+                             const void* bias, hb_stream stream);
 
 // Attention of the step's new rows over the paged cache, any sizes, on CUDA cores with 32-bit arithmetic.
 // Row b owns query rows query_start[b] .. query_start[b+1], the last ones of its kv_len[b] tokens; a query at position
@@ -160,19 +161,27 @@ int hb_latent_attention_bf16(void* out, float* scratch, const void* qa, const vo
 // [2 experts + 1] -> counts[experts + e] = first row of expert e (and the end); place[token * top + k] = the pair's
 // row, token_of[row] = its token. hb_expert_linear: out [rows, n] = act(x[token_of ? token_of[row] : row] · w[e]ᵀ) for
 // the rows of expert e, w [experts, n, k]; act 0 none, 1 relu squared, 2 silu. hb_expert_combine: out [tokens, hidden] =
-// sum_k weight[t, k] · y[place[t, k]] + (shared ? sigmoid(z[t, gate_at]) · shared[t] : 0).
+// sum_k weight[t, k] · y[place[t, k]] + (shared ? sigmoid(z[t, gate_at]) · shared[t] : 0) (z null: the shared rows are
+// added as they are); with `x` [tokens, hidden] and `identity_from` (one int32 on the device) a pair whose row is
+// *identity_from or later belongs to an identity expert and reads x[t] in place of y.
+// The choice may run on other numbers than the weights: `correction` (float [experts] or null) is added to the softmax
+// scores for the choice alone; with `groups` > 1 the experts form that many equal groups of neighbours, a group counts by
+// its best choice score and only experts of the `keep` best groups can be chosen; `tiny` is added to the chosen scores'
+// sum before `renormalize` divides by it.
 int hb_route_top(int32_t* chosen, float* weight, int32_t* counts, const float* z, const float* bias, int ld, int tokens, int experts,
-                 int top, float scale, int renormalize, hb_stream stream);
+                 int top, float scale, int renormalize, const float* correction, int groups, int keep, float tiny, hb_stream stream);
 int hb_expert_rows(int32_t* place, int32_t* token_of, int32_t* counts, const int32_t* chosen, int tokens, int top,
                    int experts, hb_stream stream);
 // hb_route_top and hb_expert_rows as one call (one launch for up to 256 tokens and 1,024 experts). counts [2 experts + 3]
 // need not be zeroed; afterwards counts[2 experts + 1 ..] = (0, tokens): the `starts` of one expert that takes every token.
 int hb_route_rows(int32_t* chosen, float* weight, int32_t* counts, int32_t* place, int32_t* token_of, const float* z,
-                  const float* bias, int ld, int tokens, int experts, int top, float scale, int renormalize, hb_stream stream);
+                  const float* bias, int ld, int tokens, int experts, int top, float scale, int renormalize,
+                  const float* correction, int groups, int keep, float tiny, hb_stream stream);
 int hb_expert_linear(void* out, const void* x, int dtype, const int32_t* token_of, const void* w, const int32_t* starts,
                      int rows, int experts, int n, int k, int act, hb_stream stream);
 int hb_expert_combine(void* out, const void* y, int dtype, const int32_t* place, const float* weight, const void* shared,
-                      const float* z, int ldz, int gate_at, int tokens, int top, int hidden, hb_stream stream);
+                      const float* z, int ldz, int gate_at, int tokens, int top, int hidden, const void* x,
+                      const int32_t* identity_from, hb_stream stream);
 // hb_expert_linear in bfloat16 on tensor cores: k and n multiples of 8; tile_rows 8 (on CUDA cores, for a row or two an expert), 16, 64 or 128 rows a tile (0: chosen
 // from the rows an expert gets on average).
 int hb_expert_linear_bf16(void* out, const void* x, const int32_t* token_of, const void* w, const int32_t* starts, int rows,
@@ -186,9 +195,23 @@ int hb_expert_linear_tcgen05(void* out, const void* x, const int32_t* token_of, 
                              const int32_t* starts, int32_t* table, int rows, int experts, int n, int k, int act,
                              hb_stream stream);
 int hb_experts_tcgen05_status(unsigned int* status);
-// x = act(x) in place (act as above); o [tokens, n] *= sigmoid(g[t * ld + i]).
-int hb_activation(void* x, int dtype, long count, int act, hb_stream stream);
+// x = act(x) in place (act as above, 3 the tanh form of gelu, 4 xielu with the two numbers `numbers`, 5 tanh);
+// o [tokens, n] *= sigmoid(g[t * ld + i]).
+int hb_activation(void* x, int dtype, long count, int act, const float* numbers, hb_stream stream);
 int hb_sigmoid_gate(void* o, const void* g, int dtype, int tokens, int n, long ld, hb_stream stream);
+// A norm without statistics, N(x) = tanh(alpha x) w + b (alpha one number on the device; alpha, w, b 32-bit), csrc/dyt.cu.
+// hb_dyt_add_norm: x = (h ? h[row] : 0) + (y ? N_post(y[row]) : 0) (post_alpha null: y as it is); without `index` and
+// with y the sum is stored in h; out[r] = N_pre(x) where out is given; index (int32 [rows]) gathers rows.
+int hb_dyt_add_norm(float* h, const void* y, int y_dtype, const float* post_alpha, const float* post_w, const float* post_b,
+                    void* out, int out_dtype, const float* pre_alpha, const float* pre_w, const float* pre_b,
+                    const int32_t* index, int rows, int dim, hb_stream stream);
+// hb_dyt_shift: x_t = h_t + N_post(y_t) -> into (which may be h itself only without y); n_t = N_pre(x_t);
+// out_t = n_t + (n_(t-1) - n_t) mix, where a row's first token takes n_(t-1) from carried [slots, dim] (32-bit) and the
+// row's last n is written there.
+int hb_dyt_shift(void* out, int out_dtype, float* into, const float* h, const void* y, int y_dtype, const float* post_alpha,
+                 const float* post_w, const float* post_b, const float* pre_alpha, const float* pre_w, const float* pre_b,
+                 const float* mix, float* carried, const int32_t* query_start, const int32_t* row_slot, int rows, int tokens,
+                 int dim, hb_stream stream);
 
 // bfloat16 product for at most 16 rows of x, bound by reading w once. mode 0: out [m, n] (bfloat16, or float32 when
 // out_f32) = x [m, k] · w [n, k]ᵀ. mode 1: w is [2 inter, k], gate rows first; out [m, inter] = silu(x · gateᵀ) ·
@@ -339,8 +362,15 @@ int hb_glu_clamped(void* out, const void* gate_up, const void* bias, int dtype, 
 // out[t, h, :] = S^T q. The state is read at the start of a row and written back at its end. `most`: no row brings more
 // tokens than this (0: unknown); it bounds the stage of tokens a block keeps in shared memory.
 int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
-                      const float* token_decay, const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
-                      int heads, int kv_heads, int dim, int vdim, int most, hb_stream stream);
+                      const float* token_decay, const float* beta, const float* rate, float* state, const int32_t* query_start,
+                      const int32_t* row_slot, int rows, int heads, int kv_heads, int dim, int vdim, int most, hb_stream stream);
+// The generalized delta rule's inputs from its first product, rows [r | k | v | g | a] of `dtype` (each heads dim wide,
+// `ld` apart) and the low-rank decay projection's output `pre` [tokens, heads dim] in 32-bit: qk = (r, k), v,
+// decay = exp(-decay_scale sigmoid(pre + decay_bias)), rate = sigmoid(a + rate_bias) / (sum_head k^2 + unit_eps); with
+// `rate` hb_recurrent_scan runs S <- diag(decay) S - (rate o k)(k^T S) + k v^T, both terms on the old S.
+int hb_gdelta_prepare(float* qk, float* v, float* decay, float* rate, const void* first, int dtype, long ld,
+                      const float* pre, const float* decay_bias, const float* rate_bias, int tokens, int heads, int dim,
+                      float decay_scale, float unit_eps, hb_stream stream);
 // A delta-rule mixer's first product, rows [q | k | v | b] of `dtype`, `ld` apart, and the outputs of its two low-rank
 // projections, low2 [tokens, heads dim + heads vdim] in 32-bit, become the scan's inputs: q, k, v through a causal
 // convolution over time (conv [channels, taps], carried inputs conv_state [slots, taps - 1, channels]) and silu; q, k
@@ -358,10 +388,12 @@ int hb_conv_carry(void* conv_state, const void* first, int dtype, int ld, int ch
 int hb_retention_prepare(float* qk, float* v, const void* first, int dtype, int ld, const int32_t* positions,
                          const float* table, int rot_dims, int max_positions, int tokens, int heads, int dim, int vdim,
                          float k_scale, hb_stream stream);
-// out [tokens, heads, vdim] (`dtype`) = o / sqrt(mean(o^2) + eps) * weight (float [vdim] or null) * gate, the gate a
-// 32-bit multiplier gate_mul [tokens, heads vdim], or silu of gate_pre (rows `ld` apart, `dtype`), or none.
+// out [tokens, heads, vdim] (`dtype`) = o / sqrt(mean(o^2) + eps) * weight (float [vdim], with `weight_heads` [heads
+// vdim], or null) * gate, the gate a 32-bit multiplier gate_mul [tokens, heads vdim], or silu (`gate_sigmoid`: sigmoid)
+// of gate_pre (rows `ld` apart, `dtype`), or none.
 int hb_head_norm_gate(void* out, const float* o, int dtype, const float* weight, const float* gate_mul,
-                      const void* gate_pre, long ld, float eps, int tokens, int heads, int vdim, hb_stream stream);
+                      const void* gate_pre, long ld, float eps, int tokens, int heads, int vdim, int weight_heads,
+                      int gate_sigmoid, hb_stream stream);
 
 // ---- the matrix memory with exponential gates (csrc/mlstm.cu): the kernels around hb_recurrent_scan with token_decay.
 // pre [tokens, ld] 32-bit: the input gate's pre-activations of the heads, then the forget gate's; bias [2 heads] likewise.

@@ -6,7 +6,7 @@
 // hb_route_top       z [tokens, ld] (32-bit logits) -> chosen [tokens, top], weight [tokens, top], counts[e] += 1
 // hb_expert_rows     counts -> first row of every expert; place[pair] = its row, token_of[row] = its token
 // hb_expert_linear   out[row] = act(x[token_of ? token_of[row] : row] · w[e(row)]ᵀ), any dtype, CUDA cores
-// hb_expert_combine  out[t] = sum_k weight[t, k] · y[place[t, k]] (+ sigmoid(gate_t) · shared[t])
+// hb_expert_combine  out[t] = sum_k weight[t, k] · y[place[t, k]] (+ sigmoid(gate_t) · shared[t]); rows of identity experts read x[t]
 #include "common.cuh"
 
 // ---------------------------------------------------------------- the router's choice
@@ -60,11 +60,112 @@ __global__ void route_top_kernel(int32_t* __restrict__ chosen, float* __restrict
     }
 }
 
+// The choice with a correction and in groups, one warp per token. sc [experts] holds the token's exponentials, inv one
+// over their sum; ch [experts] and gm [groups] are scratch of this warp. The choice runs on s + correction (which may be
+// negative: what is out of the running is minus infinity); with `groups` > 1 the experts form that many equal groups of
+// neighbours, a group counts by its best choice score, and only the `keep` best groups (equal ones by ascending group)
+// stay in the running. The weights are the chosen experts' s, with `renormalize` divided by their sum + tiny.
+__device__ __forceinline__ void route_choice_warp(int lane, const float* sc, float* ch, float* gm, float inv,
+                                                  const float* __restrict__ correction, int experts, int top, int groups,
+                                                  int keep, int32_t* chosen, float* weight, int* cnt, float scale,
+                                                  int renormalize, float tiny) {
+    for (int e = lane; e < experts; e += 32) ch[e] = sc[e] * inv + (correction ? correction[e] : 0.f);
+    __syncwarp();
+    if (groups > 1) {
+        const int per = experts / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float m = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, ch[e]);
+            gm[g] = m;
+        }
+        __syncwarp();
+        for (int r = 0; r < keep; ++r) {                     // a kept group is marked by plus infinity
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = gm[g];
+                if (v != INFINITY && (v > bv || (v == bv && g < bi))) { bv = v; bi = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+            }
+            if (lane == 0 && bi != 0x7fffffff) gm[bi] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < experts; e += 32) if (gm[e / per] != INFINITY) ch[e] = -INFINITY;
+        __syncwarp();
+    }
+    float taken = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = ch[e];
+            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        const float share = sc[bi] * inv;
+        if (lane == 0) {
+            chosen[k] = bi;
+            weight[k] = share;
+            ch[bi] = -INFINITY;
+            atomicAdd(cnt + bi, 1);
+        }
+        taken += share;
+        __syncwarp();
+    }
+    const float f = renormalize ? scale / (taken + tiny) : scale;
+    for (int k = lane; k < top; k += 32) weight[k] *= f;
+}
+
+// hb_route_top with a correction or groups: a warp a token, eight tokens a block; shared memory 3 x 8 x experts floats.
+__global__ void __launch_bounds__(256) route_choice_kernel(int32_t* __restrict__ chosen, float* __restrict__ weight,
+                                                           int32_t* __restrict__ counts, const float* __restrict__ z, int ld,
+                                                           int tokens, int experts, int top, float scale, int renormalize,
+                                                           const float* __restrict__ bias, const float* __restrict__ correction,
+                                                           int groups, int keep, float tiny) {
+    extern __shared__ float rc_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= tokens) return;
+    float* my = rc_smem + (size_t)warp * experts;
+    float* ch = rc_smem + (size_t)(8 + warp) * experts;
+    float* gm = rc_smem + (size_t)(16 + warp) * experts;
+    const float* zr = z + (size_t)t * ld;
+    float m = -INFINITY;
+    for (int e = lane; e < experts; e += 32) m = fmaxf(m, zr[e] + (bias ? bias[e] : 0.f));
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) { const float p = expf(zr[e] + (bias ? bias[e] : 0.f) - m); my[e] = p; sum += p; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    route_choice_warp(lane, my, ch, gm, 1.f / sum, correction, experts, top, groups, keep, chosen + (size_t)t * top,
+                      weight + (size_t)t * top, counts, scale, renormalize, tiny);
+}
+
 extern "C" int hb_route_top(int32_t* chosen, float* weight, int32_t* counts, const float* z, const float* bias, int ld,
-                            int tokens, int experts, int top, float scale, int renormalize, hb_stream stream) {
+                            int tokens, int experts, int top, float scale, int renormalize, const float* correction,
+                            int groups, int keep, float tiny, hb_stream stream) {
     if (tokens == 0) return 0;
     if (experts < 1 || top < 1 || top > experts || ld < experts) HB_REFUSE("route_top: top %d of %d experts in rows of %d", top, experts, ld);
     if (experts > 8192) HB_REFUSE("route_top: %d experts are above 8192", experts);
+    if (groups < 1 || experts % groups || keep < 1 || keep > groups || (long)keep * (experts / groups) < top)
+        HB_REFUSE("route_top: %d groups of which %d are kept, for top %d of %d experts", groups, keep, top, experts);
+    if (correction || groups > 1 || tiny != 0.f) {
+        const size_t smem = (size_t)24 * experts * sizeof(float);
+        if (smem > 200 * 1024) HB_REFUSE("route_top: a choice in groups takes up to 2133 experts, not %d", experts);
+        if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(route_choice_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        route_choice_kernel<<<(tokens + 7) / 8, 256, smem, (cudaStream_t)stream>>>(chosen, weight, counts, z, ld, tokens, experts, top,
+                                                                                  scale, renormalize, bias, correction, groups, keep, tiny);
+        HB_LAUNCH_CHECK("route_choice");
+        return 0;
+    }
     const int threads = experts > 256 ? 256 : experts > 64 ? 128 : 64;
     route_top_kernel<<<tokens, threads, (size_t)experts * sizeof(float), (cudaStream_t)stream>>>(
         chosen, weight, counts, z, ld, experts, top, scale, renormalize, bias);
@@ -139,7 +240,9 @@ __global__ void __launch_bounds__(256) route_rows_small_kernel(int32_t* __restri
                                                                int32_t* __restrict__ counts, int32_t* __restrict__ place,
                                                                int32_t* __restrict__ token_of, const float* __restrict__ z,
                                                                int ld, int tokens, int experts, int top, float scale,
-                                                               int renormalize, const float* __restrict__ bias) {
+                                                               int renormalize, const float* __restrict__ bias,
+                                                               const float* __restrict__ correction, int groups, int keep,
+                                                               float tiny, int grouped) {
     extern __shared__ float rs_smem[];
     float* sc = rs_smem;                                   // [8][experts]
     int* cnt = (int*)(sc + 8 * (size_t)experts);           // [experts]: counts, then cursors
@@ -158,6 +261,13 @@ __global__ void __launch_bounds__(256) route_rows_small_kernel(int32_t* __restri
         sum = warp_sum(sum);
         __syncwarp();
         const float inv = 1.f / sum;
+        if (grouped) {                                      // (scratch behind the first rows: [8][experts] twice)
+            float* extra = (float*)(start + experts + 1);
+            route_choice_warp(lane, my, extra + (size_t)warp * experts, extra + (size_t)(8 + warp) * experts, inv, correction,
+                              experts, top, groups, keep, chosen + (size_t)t * top, weight + (size_t)t * top, cnt, scale,
+                              renormalize, tiny);
+            continue;
+        }
         float taken = 0.f;
         for (int k = 0; k < top; ++k) {
             float bv = -1.f; int bi = 0x7fffffff;
@@ -207,19 +317,24 @@ __global__ void expert_whole_kernel(int32_t* counts, int experts, int tokens) {
 // 2 experts + 1, the pair (0, tokens).
 extern "C" int hb_route_rows(int32_t* chosen, float* weight, int32_t* counts, int32_t* place, int32_t* token_of,
                              const float* z, const float* bias, int ld, int tokens, int experts, int top, float scale,
-                             int renormalize, hb_stream stream) {
+                             int renormalize, const float* correction, int groups, int keep, float tiny, hb_stream stream) {
     if (tokens == 0) return 0;
     if (experts < 1 || top < 1 || top > experts || ld < experts) HB_REFUSE("route_rows: top %d of %d experts in rows of %d", top, experts, ld);
+    if (groups < 1 || experts % groups || keep < 1 || keep > groups || (long)keep * (experts / groups) < top)
+        HB_REFUSE("route_rows: %d groups of which %d are kept, for top %d of %d experts", groups, keep, top, experts);
     cudaStream_t s = (cudaStream_t)stream;
+    const int grouped = correction || groups > 1 || tiny != 0.f;
     if (tokens <= RS_TOKENS && experts <= RS_EXPERTS) {
-        const size_t smem = ((size_t)8 * experts + 2 * experts + 1) * sizeof(float);
+        const size_t smem = ((size_t)(grouped ? 24 : 8) * experts + 2 * experts + 1) * sizeof(float);
         if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(route_rows_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        route_rows_small_kernel<<<1, 256, smem, s>>>(chosen, weight, counts, place, token_of, z, ld, tokens, experts, top, scale, renormalize, bias);
+        route_rows_small_kernel<<<1, 256, smem, s>>>(chosen, weight, counts, place, token_of, z, ld, tokens, experts, top, scale,
+                                                     renormalize, bias, correction, groups, keep, tiny, grouped);
         HB_LAUNCH_CHECK("route_rows_small");
         return 0;
     }
     HB_CUDA(cudaMemsetAsync(counts, 0, (size_t)(2 * experts + 3) * sizeof(int32_t), s));
-    int rc = hb_route_top(chosen, weight, counts, z, bias, ld, tokens, experts, top, scale, renormalize, stream);
+    int rc = hb_route_top(chosen, weight, counts, z, bias, ld, tokens, experts, top, scale, renormalize, correction, groups, keep,
+                          tiny, stream);
     if (rc) return rc;
     rc = hb_expert_rows(place, token_of, counts, chosen, tokens, top, experts, stream);
     if (rc) return rc;
@@ -344,17 +459,27 @@ extern "C" int hb_expert_linear(void* out, const void* x, int dtype, const int32
 }
 
 // ---------------------------------------------------------------- elementwise
+// act 4 (xielu, with two numbers p, q): softplus(p) v^2 + v / 2 for v > 0, (1/2 + softplus(q)) (exp(v) - 1 - v) + v / 2
+// otherwise; act 5: tanh. Both for this kernel alone (the experts' products know 1 to 3).
+__device__ __forceinline__ float softplus_e(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 template <typename T>
-__global__ void activation_kernel(T* __restrict__ x, long count, int act) {
+__global__ void activation_kernel(T* __restrict__ x, long count, int act, const float* __restrict__ numbers) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < count) x[i] = from_f32<T>(expert_act(to_f32(x[i]), act));
+    if (i >= count) return;
+    const float v = to_f32(x[i]);
+    float y;
+    if (act == 4) y = v > 0.f ? fmaf(softplus_e(numbers[0]) * v, v, 0.5f * v) : fmaf(0.5f + softplus_e(numbers[1]), expm1f(v) - v, 0.5f * v);
+    else if (act == 5) y = tanhf(v);
+    else y = expert_act(v, act);
+    x[i] = from_f32<T>(y);
 }
 
-extern "C" int hb_activation(void* x, int dtype, long count, int act, hb_stream stream) {
+extern "C" int hb_activation(void* x, int dtype, long count, int act, const float* numbers, hb_stream stream) {
     if (count == 0) return 0;
+    if (act == 4 && !numbers) HB_REFUSE("activation: xielu needs its two numbers");
     const unsigned blocks = (unsigned)((count + 255) / 256);
-    if (dtype == HB_F32) activation_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)x, count, act);
-    else if (dtype == HB_BF16) activation_kernel<bf16><<<blocks, 256, 0, (cudaStream_t)stream>>>((bf16*)x, count, act);
+    if (dtype == HB_F32) activation_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)x, count, act, numbers);
+    else if (dtype == HB_BF16) activation_kernel<bf16><<<blocks, 256, 0, (cudaStream_t)stream>>>((bf16*)x, count, act, numbers);
     else HB_REFUSE("activation: dtype %d", dtype);
     HB_LAUNCH_CHECK("activation");
     return 0;
@@ -384,19 +509,22 @@ extern "C" int hb_sigmoid_gate(void* o, const void* g, int dtype, int tokens, in
 template <typename T>
 __global__ void expert_combine_kernel(T* __restrict__ out, const T* __restrict__ y, const int32_t* __restrict__ place,
                                       const float* __restrict__ weight, const T* __restrict__ shared,
-                                      const float* __restrict__ z, int ldz, int gate_at, int top, int hidden) {
+                                      const float* __restrict__ z, int ldz, int gate_at, int top, int hidden,
+                                      const T* __restrict__ x, const int32_t* __restrict__ identity_from) {
     __shared__ int rows[XC_TOP];                            // the token's rows and weights, read once
+    const int ident = identity_from ? *identity_from : 0x7fffffff;   // rows from here on belong to identity experts: x[t]
     __shared__ float wgt[XC_TOP];
     const size_t t = blockIdx.x;
     const bool kept = top <= XC_TOP;
     if (kept && threadIdx.x < top) { rows[threadIdx.x] = place[t * top + threadIdx.x]; wgt[threadIdx.x] = weight[t * top + threadIdx.x]; }
     __syncthreads();
-    const float gate = shared ? 1.f / (1.f + expf(-z[t * ldz + gate_at])) : 0.f;
+    const float gate = shared ? (z ? 1.f / (1.f + expf(-z[t * ldz + gate_at])) : 1.f) : 0.f;
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hidden; i += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
             const int p = kept ? rows[k] : place[t * top + k];
-            if (p >= 0) acc = fmaf(kept ? wgt[k] : weight[t * top + k], to_f32(y[(size_t)p * hidden + i]), acc);
+            if (p >= 0) acc = fmaf(kept ? wgt[k] : weight[t * top + k],
+                                   to_f32(p >= ident ? x[t * hidden + i] : y[(size_t)p * hidden + i]), acc);
         }
         if (shared) acc = fmaf(gate, to_f32(shared[t * hidden + i]), acc);
         out[t * hidden + i] = from_f32<T>(acc);
@@ -406,19 +534,21 @@ __global__ void expert_combine_kernel(T* __restrict__ out, const T* __restrict__
 // The same in bfloat16 for rows of a multiple of 8 columns: a thread adds 8 columns at a time (16-byte loads).
 __global__ void expert_combine_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ y, const int32_t* __restrict__ place,
                                              const float* __restrict__ weight, const bf16* __restrict__ shared,
-                                             const float* __restrict__ z, int ldz, int gate_at, int top, int hidden) {
+                                             const float* __restrict__ z, int ldz, int gate_at, int top, int hidden,
+                                             const bf16* __restrict__ x, const int32_t* __restrict__ identity_from) {
     __shared__ int rows[XC_TOP];
     __shared__ float wgt[XC_TOP];
+    const int ident = identity_from ? *identity_from : 0x7fffffff;
     const size_t t = blockIdx.x;
     if (threadIdx.x < top) { rows[threadIdx.x] = place[t * top + threadIdx.x]; wgt[threadIdx.x] = weight[t * top + threadIdx.x]; }
     __syncthreads();
-    const float gate = shared ? 1.f / (1.f + expf(-z[t * ldz + gate_at])) : 0.f;
+    const float gate = shared ? (z ? 1.f / (1.f + expf(-z[t * ldz + gate_at])) : 1.f) : 0.f;
     for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8; i < hidden; i += gridDim.y * blockDim.x * 8) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int k = 0; k < top; ++k) {
             const int p = rows[k];
             if (p < 0) continue;
-            const uint4 v = __ldg((const uint4*)(y + (size_t)p * hidden + i));
+            const uint4 v = __ldg((const uint4*)(p >= ident ? x + t * hidden + i : y + (size_t)p * hidden + i));
             const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
             const float w = wgt[k];
 #pragma unroll
@@ -440,27 +570,28 @@ __global__ void expert_combine_bf16x8_kernel(bf16* __restrict__ out, const bf16*
 
 extern "C" int hb_expert_combine(void* out, const void* y, int dtype, const int32_t* place, const float* weight,
                                  const void* shared, const float* z, int ldz, int gate_at, int tokens, int top, int hidden,
-                                 hb_stream stream) {
+                                 const void* x, const int32_t* identity_from, hb_stream stream) {
     if (tokens == 0) return 0;
-    if (shared && (!z || gate_at >= ldz)) HB_REFUSE("expert_combine: a shared expert needs its gate's logit");
+    if (shared && z && gate_at >= ldz) HB_REFUSE("expert_combine: the shared expert's gate lies outside the logits' rows");
+    if ((x == nullptr) != (identity_from == nullptr)) HB_REFUSE("expert_combine: identity experts need the input rows and their first row");
     if (hidden > 65535 * 128) HB_REFUSE("expert_combine: %d columns", hidden);
     const int threads = hidden >= 256 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(tokens, (hidden + threads - 1) / threads);                        // a block every `threads` columns of a token
-    if (dtype == HB_BF16 && hidden % 8 == 0 && top <= XC_TOP && (((uintptr_t)out | (uintptr_t)y | (uintptr_t)shared) % 16) == 0) {
+    if (dtype == HB_BF16 && hidden % 8 == 0 && top <= XC_TOP && (((uintptr_t)out | (uintptr_t)y | (uintptr_t)shared | (uintptr_t)x) % 16) == 0) {
         const int th = hidden >= 1024 ? 128 : 64;                   // 8 columns a thread
         dim3 g8(tokens, (hidden / 8 + th - 1) / th);
         expert_combine_bf16x8_kernel<<<g8, th, 0, s>>>((bf16*)out, (const bf16*)y, place, weight, (const bf16*)shared, z, ldz,
-                                                      gate_at, top, hidden);
+                                                      gate_at, top, hidden, (const bf16*)x, identity_from);
         HB_LAUNCH_CHECK("expert_combine");
         return 0;
     }
     if (dtype == HB_F32)
         expert_combine_kernel<float><<<grid, threads, 0, s>>>((float*)out, (const float*)y, place, weight,
-                                                                (const float*)shared, z, ldz, gate_at, top, hidden);
+                                                                (const float*)shared, z, ldz, gate_at, top, hidden, (const float*)x, identity_from);
     else if (dtype == HB_BF16)
         expert_combine_kernel<bf16><<<grid, threads, 0, s>>>((bf16*)out, (const bf16*)y, place, weight,
-                                                               (const bf16*)shared, z, ldz, gate_at, top, hidden);
+                                                               (const bf16*)shared, z, ldz, gate_at, top, hidden, (const bf16*)x, identity_from);
     else HB_REFUSE("expert_combine: dtype %d", dtype);
     HB_LAUNCH_CHECK("expert_combine");
     return 0;

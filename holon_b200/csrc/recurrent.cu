@@ -5,6 +5,8 @@
 //                                            decay per head)
 //     u  = beta_t (v_t - S^T k_t)           (the delta rule; without beta: u = v_t)
 //     S <- S + k_t u^T,      o_t = S^T q_t  (the read-out sees the token's own write)
+// or, with a removal rate r_t per key channel (the generalized delta rule, both terms on the old S),
+//     S <- diag(g_t) S - (r_t o k_t)(k_t^T S) + k_t v_t^T,      o_t = S^T q_t
 // and the kernels around that scan: what turns a layer's first product into q, k, v, decays and gates (a short causal
 // convolution over time with its carried inputs, activations, unit vectors, rotation), and the per-head norm with the
 // output gate behind the scan. Everything that enters the recurrence is 32-bit here, whatever the engine's dtype.
@@ -41,10 +43,12 @@ __device__ __forceinline__ void cp_async_f32x4(float* dst, const float* src) {
 }
 
 // TOKEN: `head_decay` holds one decay per token and head [tokens, heads]; it rides in the stage's beta column (no delta rule then).
-template <int DPT, int P, bool PER_CHANNEL, bool DELTA, bool TOKEN = false>
+// GENERAL (with PER_CHANNEL, without DELTA): `rate` [tokens, heads, dim] is the removal rate per key channel; a fourth
+// array of the stage holds it, and a token's step is S_i <- g_i S_i + k_i (v - r_i (k . S_old)).
+template <int DPT, int P, bool PER_CHANNEL, bool DELTA, bool TOKEN = false, bool GENERAL = false>
 __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qk, const float* __restrict__ v,
                                       const float* __restrict__ decay, const float* __restrict__ head_decay,
-                                      const float* __restrict__ beta, float* __restrict__ state,
+                                      const float* __restrict__ beta, const float* __restrict__ rate, float* __restrict__ state,
                                       const int32_t* __restrict__ query_start, const int32_t* __restrict__ row_slot,
                                       int heads, int kv_heads, int dim, int vdim, int VT, int tb) {
     extern __shared__ __align__(16) float sm[];
@@ -76,6 +80,37 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
         const float* k_g = qk + ((t * 2 + 1) * kv_heads + hk) * dim;
         float u = col ? v[(t * heads + h) * vdim + c] : 0.f;
         float4 k4[DPT / 4], q4[DPT / 4];
+        if (GENERAL) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                k4[i] = four(k_g, (i * P + p) * 4, 0.f);
+                a += S[4 * i] * k4[i].x + S[4 * i + 1] * k4[i].y + S[4 * i + 2] * k4[i].z + S[4 * i + 3] * k4[i].w;
+            }
+#pragma unroll
+            for (int o = 1; o < P; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const int d = (i * P + p) * 4;
+                const float4 g = four(decay + (t * heads + h) * dim, d, 1.f), r = four(rate + (t * heads + h) * dim, d, 0.f);
+                const float4 q = four(q_g, d, 0.f);
+                S[4 * i] = fmaf(g.x, S[4 * i], k4[i].x * fmaf(-r.x, a, u));
+                S[4 * i + 1] = fmaf(g.y, S[4 * i + 1], k4[i].y * fmaf(-r.y, a, u));
+                S[4 * i + 2] = fmaf(g.z, S[4 * i + 2], k4[i].z * fmaf(-r.z, a, u));
+                S[4 * i + 3] = fmaf(g.w, S[4 * i + 3], k4[i].w * fmaf(-r.w, a, u));
+                o += S[4 * i] * q.x + S[4 * i + 1] * q.y + S[4 * i + 2] * q.z + S[4 * i + 3] * q.w;
+            }
+#pragma unroll
+            for (int x = 1; x < P; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+            if (p == 0 && col) out[(t * heads + h) * vdim + c] = o;
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = ((i >> 2) * P + p) * 4 + (i & 3);
+                if (col && d < dim) S_g[d] = S[i];
+            }
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < DPT / 4; ++i) {
             const int d = (i * P + p) * 4;
@@ -116,7 +151,8 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
         }
         return;
     }
-    const int used = tb * ((PER_CHANNEL ? 3 : 2) * DP + VT + 1), per_stage = (used + 3) & ~3;   // (stages start on 16-byte boundaries)
+    constexpr int ARRAYS = PER_CHANNEL ? (GENERAL ? 4 : 3) : 2;       // q, k, decays, removal rates
+    const int used = tb * (ARRAYS * DP + VT + 1), per_stage = (used + 3) & ~3;   // (stages start on 16-byte boundaries)
     for (int e = threadIdx.x; e < 2 * per_stage; e += blockDim.x) {      // what no copy fills stays neutral: k = q = v = 0,
         const int at = e % per_stage;                                    // decay = beta = 1
         const bool one = (PER_CHANNEL && at >= 2 * tb * DP && at < 3 * tb * DP) || (at >= used - tb && at < used);
@@ -129,7 +165,8 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
         float* sq = sm + which * per_stage;
         float* sk = sq + tb * DP;
         float* sg = sk + tb * DP;
-        float* sv = sg + (PER_CHANNEL ? tb * DP : 0);
+        float* sr = sg + tb * DP;
+        float* sv = sk + (ARRAYS - 1) * tb * DP;
         float* sb = sv + tb * VT;
         const int m = min(tb, n - j0);
         if (vec) {
@@ -140,6 +177,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                 cp_async_f32x4(sq + j * DP + d, qk + ((t * 2) * kv_heads + hk) * dim + d);
                 cp_async_f32x4(sk + j * DP + d, qk + ((t * 2 + 1) * kv_heads + hk) * dim + d);
                 if (PER_CHANNEL) cp_async_f32x4(sg + j * DP + d, decay + (t * heads + h) * dim + d);
+                if (GENERAL) cp_async_f32x4(sr + j * DP + d, rate + (t * heads + h) * dim + d);
             }
         } else {
             for (int e = threadIdx.x; e < m * dim; e += blockDim.x) {
@@ -148,6 +186,7 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
                 cp_async_f32(sq + j * DP + d, qk + ((t * 2) * kv_heads + hk) * dim + d);
                 cp_async_f32(sk + j * DP + d, qk + ((t * 2 + 1) * kv_heads + hk) * dim + d);
                 if (PER_CHANNEL) cp_async_f32(sg + j * DP + d, decay + (t * heads + h) * dim + d);
+                if (GENERAL) cp_async_f32(sr + j * DP + d, rate + (t * heads + h) * dim + d);
             }
         }
         for (int e = threadIdx.x; e < m * width; e += blockDim.x) {
@@ -175,7 +214,8 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
         const float* sq = sm + which * per_stage;
         const float* sk = sq + tb * DP;
         const float* sg = sk + tb * DP;
-        const float* sv = sg + (PER_CHANNEL ? tb * DP : 0);
+        const float* sr = sg + tb * DP;
+        const float* sv = sk + (ARRAYS - 1) * tb * DP;
         const float* sb = sv + tb * VT;
 #pragma unroll 2
         for (int j = 0; j < m; ++j) {
@@ -185,6 +225,37 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
             float4 k4[DPT / 4];
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) k4[i] = kj[i * P];
+            if (GENERAL) {                                           // k . S on the state as it was, then decay, removal and write
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    a0 = fmaf(S[4 * i], k4[i].x, a0); a1 = fmaf(S[4 * i + 1], k4[i].y, a1);
+                    a0 = fmaf(S[4 * i + 2], k4[i].z, a0); a1 = fmaf(S[4 * i + 3], k4[i].w, a1);
+                }
+                float a = a0 + a1;
+#pragma unroll
+                for (int o = 1; o < P; o <<= 1) {
+                    a += __shfl_xor_sync(0xffffffffu, a, o);
+                    o_before += __shfl_xor_sync(0xffffffffu, o_before, o);
+                }
+                if (at_before >= 0 && p == 0 && col) out[((size_t)at_before * heads + h) * vdim + c] = o_before;
+                const float4* gj = (const float4*)(sg + j * DP) + p;
+                const float4* rj = (const float4*)(sr + j * DP) + p;
+                float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    const float4 g = gj[i * P], r = rj[i * P], q4 = qj[i * P];
+                    S[4 * i] = fmaf(g.x, S[4 * i], k4[i].x * fmaf(-r.x, a, u));
+                    S[4 * i + 1] = fmaf(g.y, S[4 * i + 1], k4[i].y * fmaf(-r.y, a, u));
+                    S[4 * i + 2] = fmaf(g.z, S[4 * i + 2], k4[i].z * fmaf(-r.z, a, u));
+                    S[4 * i + 3] = fmaf(g.w, S[4 * i + 3], k4[i].w * fmaf(-r.w, a, u));
+                    o0 = fmaf(S[4 * i], q4.x, o0); o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                    o0 = fmaf(S[4 * i + 2], q4.z, o0); o1 = fmaf(S[4 * i + 3], q4.w, o1);
+                }
+                o_before = o0 + o1;
+                at_before = t0 + j0 + j;
+                continue;
+            }
             if (PER_CHANNEL) {
                 const float4* gj = (const float4*)(sg + j * DP) + p;
 #pragma unroll
@@ -244,14 +315,14 @@ __global__ void recurrent_scan_kernel(float* __restrict__ out, const float* __re
 
 template <int DPT, int P>
 static int launch_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
-                       const float* token_decay, const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
+                       const float* token_decay, const float* beta, const float* rate, float* state, const int32_t* query_start, const int32_t* row_slot, int rows,
                        int heads, int kv_heads, int dim, int vdim, int most, cudaStream_t s) {
     const int unit = 32 / P > 1 ? 32 / P : 1;                         // columns a warp holds
     int VT = vdim < 256 / P ? vdim : 256 / P;
     if (VT < 1) VT = 1;
     const int threads = ((VT + unit - 1) / unit) * unit * P;
     const int tiles = (vdim + VT - 1) / VT;
-    const int per_token = (decay ? 3 : 2) * P * DPT + VT + 1;
+    const int per_token = (decay ? (rate ? 4 : 3) : 2) * P * DPT + VT + 1;
     int tb = 96 * 1024 / 8 / per_token;                               // two stages in at most 96 KB
     if (tb > SC_TB) tb = SC_TB;
     if (tb < 1) HB_REFUSE("recurrent_scan: key size %d needs more shared memory than a block has", dim);
@@ -261,25 +332,27 @@ static int launch_scan(float* out, const float* qk, const float* v, const float*
     auto kernel = decay ? (beta ? recurrent_scan_kernel<DPT, P, true, true> : recurrent_scan_kernel<DPT, P, true, false>)
                         : (beta ? recurrent_scan_kernel<DPT, P, false, true> : recurrent_scan_kernel<DPT, P, false, false>);
     if (token_decay) { kernel = recurrent_scan_kernel<DPT, P, false, false, true>; head_decay = token_decay; }
+    if (rate) kernel = recurrent_scan_kernel<DPT, P, true, false, false, true>;
     if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kernel<<<dim3(rows, heads, tiles), threads, smem, s>>>(out, qk, v, decay, head_decay, beta, state, query_start, row_slot,
+    kernel<<<dim3(rows, heads, tiles), threads, smem, s>>>(out, qk, v, decay, head_decay, beta, rate, state, query_start, row_slot,
                                                           heads, kv_heads, dim, vdim, VT, tb);
     HB_LAUNCH_CHECK("recurrent_scan");
     return 0;
 }
 
 extern "C" int hb_recurrent_scan(float* out, const float* qk, const float* v, const float* decay, const float* head_decay,
-                                 const float* token_decay, const float* beta, float* state, const int32_t* query_start, const int32_t* row_slot,
+                                 const float* token_decay, const float* beta, const float* rate, float* state, const int32_t* query_start, const int32_t* row_slot,
                                  int rows, int heads, int kv_heads, int dim, int vdim, int most, hb_stream stream) {
     if (rows == 0) return 0;
     if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("recurrent_scan: %d heads are no multiple of %d key heads", heads, kv_heads);
     if (dim < 1 || dim > 1024 || vdim < 1) HB_REFUSE("recurrent_scan: key size %d (1 to 1024), value size %d", dim, vdim);
     if ((decay != nullptr) + (head_decay != nullptr) + (token_decay != nullptr) != 1) HB_REFUSE("recurrent_scan: give decays per channel and token, per head and token, or one per head");
     if (token_decay && beta) HB_REFUSE("recurrent_scan: the delta rule does not go with a decay per head and token");
+    if (rate && (!decay || beta)) HB_REFUSE("recurrent_scan: removal rates per key channel go with decays per key channel and without beta");
     if (rows > 65535 * 32 || heads > 65535 || (vdim + 7) / 8 > 65535) HB_REFUSE("recurrent_scan: %d rows, %d heads, value size %d", rows, heads, vdim);
-    if ((((uintptr_t)qk | (uintptr_t)decay) & 15) != 0) HB_REFUSE("recurrent_scan: qk and decay must lie on 16-byte boundaries");
+    if ((((uintptr_t)qk | (uintptr_t)decay | (uintptr_t)rate) & 15) != 0) HB_REFUSE("recurrent_scan: qk, decay and rate must lie on 16-byte boundaries");
     cudaStream_t s = (cudaStream_t)stream;
-#define HB_SCAN(D, PP) return launch_scan<D, PP>(out, qk, v, decay, head_decay, token_decay, beta, state, query_start, row_slot, rows, heads, \
+#define HB_SCAN(D, PP) return launch_scan<D, PP>(out, qk, v, decay, head_decay, token_decay, beta, rate, state, query_start, row_slot, rows, heads, \
                                                  kv_heads, dim, vdim, most, s)
     // Four channels a thread up to a key size of 64, then more channels a thread. (Key size 128, 2,048 tokens of 16 heads,
     // microseconds a token with the delta rule: 16 lanes of 8 channels 0.37, 32 lanes of 4 0.40, 8 lanes of 16 0.40, 4 lanes of
@@ -446,13 +519,13 @@ extern "C" int hb_retention_prepare(float* qk, float* v, const void* first, int 
 }
 
 // ---------------------------------------------------------------- per-head norm and output gate behind the scan
-// out[t, h, :] = o / sqrt(mean(o^2) + eps) * weight * gate. `weight` [vdim] or null; the gate is either a ready
-// multiplier in 32-bit (gate_mul [tokens, heads vdim]) or silu of a pre-activation in the engine's dtype (gate_pre, rows
-// `ld` apart). One warp per (token, head).
+// out[t, h, :] = o / sqrt(mean(o^2) + eps) * weight * gate. `weight` [vdim], [heads vdim] (`weight_heads`) or null; the
+// gate is either a ready multiplier in 32-bit (gate_mul [tokens, heads vdim]) or silu (`gate_sigmoid`: sigmoid) of a
+// pre-activation in the engine's dtype (gate_pre, rows `ld` apart). One warp per (token, head).
 template <typename T>
 __global__ void head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const float* __restrict__ weight,
                                       const float* __restrict__ gate_mul, const T* __restrict__ gate_pre, long ld,
-                                      float eps, long items, int heads, int vdim) {
+                                      float eps, long items, int heads, int vdim, int weight_heads, int gate_sigmoid) {
     const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= items) return;
     const int lane = threadIdx.x & 31;
@@ -464,23 +537,74 @@ __global__ void head_norm_gate_kernel(T* __restrict__ out, const float* __restri
     const float f = rsqrtf(warp_sum(ss) / vdim + eps);
     for (int d = lane; d < vdim; d += 32) {
         float y = x[d] * f;
-        if (weight) y *= weight[d];
+        if (weight) y *= weight[weight_heads ? h * vdim + d : d];
         if (gate_mul) y *= gate_mul[item * vdim + d];
-        else if (gate_pre) y *= silu_f(to_f32(gate_pre[t * ld + (long)h * vdim + d]));
+        else if (gate_pre) {
+            const float g = to_f32(gate_pre[t * ld + (long)h * vdim + d]);
+            y *= gate_sigmoid ? sigmoid_f(g) : silu_f(g);
+        }
         out[item * vdim + d] = from_f32<T>(y);
     }
 }
 
 extern "C" int hb_head_norm_gate(void* out, const float* o, int dtype, const float* weight, const float* gate_mul,
                                  const void* gate_pre, long ld, float eps, int tokens, int heads, int vdim,
-                                 hb_stream stream) {
+                                 int weight_heads, int gate_sigmoid, hb_stream stream) {
     const long items = (long)tokens * heads;
     if (items == 0) return 0;
     const unsigned blocks = (unsigned)((items + 3) / 4);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == HB_F32) head_norm_gate_kernel<float><<<blocks, 128, 0, s>>>((float*)out, o, weight, gate_mul, (const float*)gate_pre, ld, eps, items, heads, vdim);
-    else if (dtype == HB_BF16) head_norm_gate_kernel<bf16><<<blocks, 128, 0, s>>>((bf16*)out, o, weight, gate_mul, (const bf16*)gate_pre, ld, eps, items, heads, vdim);
+    if (dtype == HB_F32) head_norm_gate_kernel<float><<<blocks, 128, 0, s>>>((float*)out, o, weight, gate_mul, (const float*)gate_pre, ld, eps, items, heads, vdim, weight_heads, gate_sigmoid);
+    else if (dtype == HB_BF16) head_norm_gate_kernel<bf16><<<blocks, 128, 0, s>>>((bf16*)out, o, weight, gate_mul, (const bf16*)gate_pre, ld, eps, items, heads, vdim, weight_heads, gate_sigmoid);
     else HB_REFUSE("head_norm_gate: dtype %d", dtype);
     HB_LAUNCH_CHECK("head_norm_gate");
+    return 0;
+}
+
+// ---------------------------------------------------------------- what the generalized delta rule's first product becomes
+// A token's row of `first` holds [r | k | v | g | a], each heads dim wide, `ld` apart; `pre` (32-bit) [tokens, heads dim] is
+// the low-rank pair's output. qk = (r, k) and v in 32-bit; decay = exp(-decay_scale sigmoid(pre + decay_bias));
+// rate = sigmoid(a + rate_bias) / (sum over the head of k^2 + unit_eps): the removal along the unit key, as a factor on k.
+// One warp per (token, head).
+template <typename T>
+__global__ void gdelta_prepare_kernel(float* __restrict__ qk, float* __restrict__ v, float* __restrict__ decay,
+                                      float* __restrict__ rate, const T* __restrict__ first, long ld,
+                                      const float* __restrict__ pre, const float* __restrict__ decay_bias,
+                                      const float* __restrict__ rate_bias, long items, int heads, int dim,
+                                      float decay_scale, float unit_eps) {
+    const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int lane = threadIdx.x & 31;
+    const long t = item / heads;
+    const int h = (int)(item - t * heads);
+    const long n = (long)heads * dim;
+    const T* row = first + t * ld + (long)h * dim;
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) { const float k = to_f32(row[n + d]); ss = fmaf(k, k, ss); }
+    const float inv = 1.f / (warp_sum(ss) + unit_eps);
+    float* q_out = qk + ((t * 2) * heads + h) * dim;
+    float* k_out = qk + ((t * 2 + 1) * heads + h) * dim;
+    for (int d = lane; d < dim; d += 32) {
+        const long at = item * dim + d;
+        q_out[d] = to_f32(row[d]);
+        k_out[d] = to_f32(row[n + d]);
+        v[at] = to_f32(row[2 * n + d]);
+        decay[at] = expf(-decay_scale * sigmoid_f(pre[at] + decay_bias[h * dim + d]));
+        rate[at] = sigmoid_f(to_f32(row[4 * n + d]) + rate_bias[h * dim + d]) * inv;
+    }
+}
+
+extern "C" int hb_gdelta_prepare(float* qk, float* v, float* decay, float* rate, const void* first, int dtype, long ld,
+                                 const float* pre, const float* decay_bias, const float* rate_bias, int tokens, int heads,
+                                 int dim, float decay_scale, float unit_eps, hb_stream stream) {
+    const long items = (long)tokens * heads;
+    if (items == 0) return 0;
+    if (heads < 1 || dim < 1 || ld < 5L * heads * dim) HB_REFUSE("gdelta_prepare: %d heads of %d in rows of %ld", heads, dim, ld);
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == HB_F32) gdelta_prepare_kernel<float><<<blocks, 128, 0, s>>>(qk, v, decay, rate, (const float*)first, ld, pre, decay_bias, rate_bias, items, heads, dim, decay_scale, unit_eps);
+    else if (dtype == HB_BF16) gdelta_prepare_kernel<bf16><<<blocks, 128, 0, s>>>(qk, v, decay, rate, (const bf16*)first, ld, pre, decay_bias, rate_bias, items, heads, dim, decay_scale, unit_eps);
+    else HB_REFUSE("gdelta_prepare: dtype %d", dtype);
+    HB_LAUNCH_CHECK("gdelta_prepare");
     return 0;
 }

@@ -1,5 +1,6 @@
 // q/k RMSNorm per head + rotation + write of keys and values into the paged cache, one kernel.
-// One warp per (token, head): query heads first, then key heads, then value heads (a plain copy).
+// One warp per (token, head): query heads first, then key heads, then value heads (a plain copy). With `bias` (one
+// vector over a row of qkv, in its dtype) every head's numbers get theirs added first, in 32-bit.
 #include "common.cuh"
 
 template <typename T> struct Pair;
@@ -19,7 +20,8 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
                                              int rotary_dim, int max_positions, const TW* __restrict__ q_weight,
                                              const TW* __restrict__ k_weight, float eps, float offset,
                                              T* __restrict__ kv, const int32_t* __restrict__ write_index, int pages,
-                                             int page_size, int heads, int kv_heads, int head_dim) {
+                                             int page_size, int heads, int kv_heads, int head_dim,
+                                             const T* __restrict__ bias) {
     extern __shared__ float smem[];
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -29,6 +31,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
     __syncwarp();                                    // the buffer y is reused from one head to the next
     const int width = (heads + 2 * kv_heads) * head_dim;
     const T* src = qkv + (size_t)t * width + (size_t)item * head_dim;       // q heads, k heads, v heads in a row
+    const T* add = bias ? bias + (size_t)item * head_dim : nullptr;
 
     T* dst;
     const TW* weight = nullptr;
@@ -52,14 +55,16 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
     if (VEC) {
         if (!rotate) {                               // values: copied as they are
             for (int d = lane * 2; d < head_dim; d += 64) {
-                const float2 v = Pair<T>::load(src + d);        // (to 32-bit and back is exact)
+                float2 v = Pair<T>::load(src + d);              // (to 32-bit and back is exact)
+                if (add) { const float2 a = Pair<T>::load(add + d); v.x += a.x; v.y += a.y; }
                 Pair<T>::store(dst + d, v.x, v.y);
             }
             continue;
         }
         float ss = 0.f;
         for (int d = lane * 2; d < head_dim; d += 64) {
-            const float2 v = Pair<T>::load(src + d);
+            float2 v = Pair<T>::load(src + d);
+            if (add) { const float2 a = Pair<T>::load(add + d); v.x += a.x; v.y += a.y; }
             y[d] = v.x; y[d + 1] = v.y;
             ss += v.x * v.x + v.y * v.y;
         }
@@ -86,12 +91,12 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
         continue;
     }
     if (!rotate) {                                   // values: copied as they are
-        for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
+        for (int d = lane; d < head_dim; d += 32) dst[d] = add ? from_f32<T>(to_f32(src[d]) + to_f32(add[d])) : src[d];
         continue;
     }
     float ss = 0.f;
     for (int d = lane; d < head_dim; d += 32) {
-        const float v = to_f32(src[d]);
+        const float v = to_f32(src[d]) + (add ? to_f32(add[d]) : 0.f);
         y[d] = v;
         ss += v * v;
     }
@@ -225,11 +230,11 @@ template <typename T, typename TW>
 static int launch(void* q_out, const void* qkv, const int32_t* positions, const float* table, int rotary_dim,
                   int max_positions, const void* qw, const void* kw, float eps, float offset, void* kv,
                   const int32_t* write_index, int pages, int page_size, int tokens, int heads, int kv_heads,
-                  int head_dim, cudaStream_t s) {
+                  int head_dim, const void* bias, cudaStream_t s) {
     const int items = heads + (kv ? 2 * kv_heads : 0);
     if constexpr (sizeof(T) == 2) {
         const bool aligned = (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)table | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)kv) % 16) == 0;
-        if (head_dim == 128 && rotary_dim == 128 && aligned && (long)tokens * items < (1l << 31)) {
+        if (head_dim == 128 && rotary_dim == 128 && aligned && !bias && (long)tokens * items < (1l << 31)) {
             const unsigned blocks = (unsigned)(((long)tokens * items + 31) / 32);
             qk_norm_rope_kv_write_d128_kernel<TW><<<blocks, 256, 0, s>>>(
                 (bf16*)q_out, (const bf16*)qkv, positions, table, max_positions, (const TW*)qw, (const TW*)kw, eps, offset,
@@ -244,11 +249,12 @@ static int launch(void* q_out, const void* qkv, const int32_t* positions, const 
     dim3 grid(tokens, tokens >= 256 ? 1 : (items + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     const bool vec = head_dim % 4 == 0 && rotary_dim % 4 == 0 &&
-                     (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)table | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)kv) % 8 == 0);
+                     (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)table | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)kv |
+                       (uintptr_t)bias) % 8 == 0);
     auto kernel = vec ? qk_norm_rope_kv_write_kernel<T, TW, true> : qk_norm_rope_kv_write_kernel<T, TW, false>;
     kernel<<<grid, warps * 32, smem, s>>>(
         (T*)q_out, (const T*)qkv, positions, table, rotary_dim, max_positions, (const TW*)qw, (const TW*)kw, eps,
-        offset, (T*)kv, write_index, pages, page_size, heads, kv_heads, head_dim);
+        offset, (T*)kv, write_index, pages, page_size, heads, kv_heads, head_dim, (const T*)bias);
     HB_LAUNCH_CHECK("qk_norm_rope_kv_write");
     return 0;
 }
@@ -257,7 +263,7 @@ extern "C" int hb_qk_norm_rope_kv_write(void* q_out, const void* qkv, int dtype,
                                         const float* table, int rotary_dim, int max_positions, const void* q_weight,
                                         const void* k_weight, int weight_dtype, float eps, float offset, void* kv,
                                         const int32_t* write_index, int pages, int page_size, int tokens, int heads,
-                                        int kv_heads, int head_dim, hb_stream stream) {
+                                        int kv_heads, int head_dim, const void* bias, hb_stream stream) {
     if (tokens == 0) return 0;
     if (head_dim > 2048) HB_REFUSE("qk_norm_rope_kv_write: head_dim %d is above 2048", head_dim);
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
@@ -267,7 +273,7 @@ extern "C" int hb_qk_norm_rope_kv_write(void* q_out, const void* qkv, int dtype,
     if (kv && !write_index) HB_REFUSE("qk_norm_rope_kv_write: writing the cache needs write_index");
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_ARGS q_out, qkv, positions, table, rotary_dim, max_positions, q_weight, k_weight, eps, offset, kv, \
-    write_index, pages, page_size, tokens, heads, kv_heads, head_dim, s
+    write_index, pages, page_size, tokens, heads, kv_heads, head_dim, bias, s
     if (dtype == HB_F32 && weight_dtype == HB_F32) return launch<float, float>(HB_ARGS);
     if (dtype == HB_BF16 && weight_dtype == HB_BF16) return launch<bf16, bf16>(HB_ARGS);
     if (dtype == HB_BF16 && weight_dtype == HB_F32) return launch<bf16, float>(HB_ARGS);

@@ -332,9 +332,12 @@ class CudaKernels:
         self._call("hb_silu_mul", self._p(out), self._p(gate_up), _code(out), out.shape[0], out.shape[1])
 
     def qk_norm_rope_kv_write(self, q_out, qkv, positions, table, rotary_dim, q_weight, k_weight, eps, offset, kv,
-                              write_index, heads, kv_heads, head_dim) -> None:
-        self._check(q_out, qkv, positions, table, q_weight, k_weight, kv, write_index)
+                              write_index, heads, kv_heads, head_dim, bias=None) -> None:
+        """`bias` (qkv's dtype, [(heads + 2 kv_heads) head_dim], or None) is added to q, k and v first."""
+        self._check(q_out, qkv, positions, table, q_weight, k_weight, kv, write_index, bias)
         t = qkv.shape[0]
+        if bias is not None and (bias.shape != (qkv.shape[1],) or bias.dtype != qkv.dtype):
+            raise KernelError("qk_norm_rope_kv_write: bias must be one row of qkv's width and dtype")
         if qkv.shape != (t, (heads + 2 * kv_heads) * head_dim) or q_out.shape != (t, heads, head_dim) \
                 or q_out.dtype != qkv.dtype:
             raise KernelError("qk_norm_rope_kv_write: qkv must be [tokens, (heads + 2 kv_heads) head_dim], q_out "
@@ -348,7 +351,7 @@ class CudaKernels:
                    table.shape[0] if table is not None else 0, self._p(q_weight), self._p(k_weight),
                    _code(q_weight) if q_weight is not None else 0, ctypes.c_float(eps), ctypes.c_float(offset),
                    self._p(kv), self._i32(write_index, "write_index"), kv.shape[0] if kv is not None else 0,
-                   kv.shape[3] if kv is not None else 1, t, heads, kv_heads, head_dim)
+                   kv.shape[3] if kv is not None else 1, t, heads, kv_heads, head_dim, self._p(bias))
 
     def qkv_rope(self, q_out, x, weight, positions, table, rotary_dim, q_weight, k_weight, eps, offset, kv,
                  write_index, heads, kv_heads, head_dim) -> bool:
@@ -863,27 +866,39 @@ class CudaKernels:
             raise KernelError("sigmoid_gate: g must have o's shape and dtype, innermost stride 1")
         self._call("hb_sigmoid_gate", self._p(o), self._p(g), _code(o), o.shape[0], o.shape[1], ctypes.c_long(g.stride(0)))
 
-    def activation(self, x, act: int) -> None:
-        self._check(x)
-        self._call("hb_activation", self._p(x), _code(x), ctypes.c_long(x.numel()), int(act))
+    def activation(self, x, act: int, numbers=None) -> None:
+        """x = act(x) in place; `numbers` (float32 [2]) for act 4 (xielu)."""
+        self._check(x, numbers)
+        self._f32("activation", numbers)
+        if numbers is not None and numbers.numel() != 2:
+            raise KernelError("activation: xielu takes two numbers")
+        self._call("hb_activation", self._p(x), _code(x), ctypes.c_long(x.numel()), int(act), self._p(numbers))
 
-    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize, bias=None) -> None:
-        """`bias` (float32 [experts] or None) is added to the logits before anything else."""
-        self._check(chosen, weight, counts, z, bias)
-        self._f32("route_top", bias)
+    def route_top(self, chosen, weight, counts, z, experts, scale, renormalize, bias=None, correction=None, groups=1,
+                  keep=1, tiny=0.0) -> None:
+        """`bias` (float32 [experts] or None) is added to the logits before anything else. `correction` (float32 [experts]
+        or None) is added to the softmax scores for the choice alone; `groups` > 1: experts in that many equal groups of
+        neighbours, of which the `keep` best (by their best choice score) stay in the running; `tiny` is added to the
+        chosen scores' sum before `renormalize` divides."""
+        self._check(chosen, weight, counts, z, bias, correction)
+        self._f32("route_top", bias, correction)
         t, top = chosen.shape
         if z.dtype != torch.float32 or z.shape[0] != t or z.shape[1] < experts or weight.shape != (t, top) \
                 or weight.dtype != torch.float32 or counts.shape[0] < 2 * experts + 1:
             raise KernelError("route_top: z float32 [tokens, >= experts], chosen int32 and weight float32 [tokens, top], "
                               "counts int32 [2 experts + 1]")
         self._call("hb_route_top", self._i32(chosen, "chosen"), self._p(weight), self._i32(counts, "counts"), self._p(z),
-                   self._p(bias), z.shape[1], t, int(experts), top, ctypes.c_float(scale), int(bool(renormalize)))
+                   self._p(bias), z.shape[1], t, int(experts), top, ctypes.c_float(scale), int(bool(renormalize)),
+                   self._p(correction), int(groups), int(keep), ctypes.c_float(tiny))
 
-    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize, bias=None) -> None:
+    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize, bias=None,
+                   correction=None, groups=1, keep=1, tiny=0.0) -> None:
         """`route_top` and `expert_rows` as one call (one launch for a few tokens). counts int32 [2 experts + 3] need not
         be zeroed; afterwards counts[2 experts + 1:] = (0, tokens)."""
-        self._check(chosen, weight, counts, place, token_of, z, bias)
-        self._f32("route_rows", bias)
+        self._check(chosen, weight, counts, place, token_of, z, bias, correction)
+        self._f32("route_rows", bias, correction)
+        if correction is not None and correction.shape != (experts,):
+            raise KernelError("route_rows: correction must be float32 [experts]")
         t, top = chosen.shape
         if z.dtype != torch.float32 or z.shape[0] != t or z.shape[1] < experts or weight.shape != (t, top) \
                 or weight.dtype != torch.float32 or counts.shape[0] < 2 * experts + 3 or place.shape[0] != t * top \
@@ -892,7 +907,7 @@ class CudaKernels:
                               "counts int32 [2 experts + 3], place and token_of int32 [tokens * top]")
         self._call("hb_route_rows", self._i32(chosen, "chosen"), self._p(weight), self._i32(counts, "counts"),
                    self._i32(place, "place"), self._i32(token_of, "token_of"), self._p(z), self._p(bias), z.shape[1], t, int(experts), top,
-                   ctypes.c_float(scale), int(bool(renormalize)))
+                   ctypes.c_float(scale), int(bool(renormalize)), self._p(correction), int(groups), int(keep), ctypes.c_float(tiny))
 
     def expert_rows(self, place, token_of, counts, chosen, experts) -> None:
         self._check(place, token_of, counts, chosen)
@@ -927,16 +942,20 @@ class CudaKernels:
         self._call("hb_expert_linear", self._p(out), self._p(x), _code(x), self._i32(token_of, "token_of"), self._p(w),
                    self._i32(starts, "starts"), rows, e, n, k, int(act))
 
-    def expert_combine(self, out, y, place, weight, shared, z, experts) -> None:
-        self._check(out, y, place, weight, shared, z)
+    def expert_combine(self, out, y, place, weight, shared, z, experts, x=None, identity_from=None) -> None:
+        """`z` None with `shared`: the shared rows are added without a gate. `x` [tokens, hidden] and `identity_from`
+        (int32 [1] on the device): pairs whose row is identity_from[0] or later read x[token] in place of y."""
+        self._check(out, y, place, weight, shared, z, x, identity_from)
         t, hidden = out.shape
         top = weight.shape[1]
         if y.shape != (t * top, hidden) or y.dtype != out.dtype or place.shape[0] != t * top \
-                or (shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype or z is None
-                                            or z.dtype != torch.float32 or z.shape[1] <= experts)):
-            raise KernelError("expert_combine: y [tokens * top, hidden], shared [tokens, hidden], z float32 [tokens, > experts]")
+                or (shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype))\
+                or (z is not None and (z.dtype != torch.float32 or z.shape[1] <= experts)) \
+                or (x is None) != (identity_from is None) or (x is not None and (x.shape != out.shape or x.dtype != out.dtype)):
+            raise KernelError("expert_combine: y [tokens * top, hidden], shared and x [tokens, hidden], z float32 [tokens, > experts]")
         self._call("hb_expert_combine", self._p(out), self._p(y), _code(out), self._i32(place, "place"), self._p(weight),
-                   self._p(shared), self._p(z), z.shape[1] if z is not None else 0, int(experts), t, top, hidden)
+                   self._p(shared), self._p(z), z.shape[1] if z is not None else 0, int(experts), t, top, hidden,
+                   self._p(x), self._i32(identity_from, "identity_from"))
 
     # ---- a block whose parts run side by side, an embedding with a pair table, mixers with a matrix state per head
     def embed_pair(self, out, table, scale, pair, ids, positions, rows, prev, mul_prev, mul_cur, buckets) -> None:
@@ -993,10 +1012,13 @@ class CudaKernels:
             if t is not None and t.dtype != torch.float32:
                 raise KernelError(f"{what}: 32-bit tensors expected, got {t.dtype}")
 
-    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows, token_decay=None) -> None:
-        """The token-by-token update of a matrix state per head (csrc/api.h: hb_recurrent_scan)."""
-        self._check(out, qk, v, decay, head_decay, beta, state, rows.query_start, rows.row_slot, token_decay)
-        self._f32("recurrent_scan", out, qk, v, decay, head_decay, beta, state, token_decay)
+    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows, token_decay=None, rate=None) -> None:
+        """The token-by-token update of a matrix state per head (csrc/api.h: hb_recurrent_scan). `rate` (float32 [tokens,
+        heads, dim], with `decay`, without `beta`): the generalized delta rule, S ← diag(decay) S − (rate ∘ k)(kᵀ S) + k vᵀ."""
+        self._check(out, qk, v, decay, head_decay, beta, state, rows.query_start, rows.row_slot, token_decay, rate)
+        self._f32("recurrent_scan", out, qk, v, decay, head_decay, beta, state, token_decay, rate)
+        if rate is not None and (decay is None or rate.shape != decay.shape):
+            raise KernelError("recurrent_scan: rate goes with decay and has its shape")
         t, heads, vdim = v.shape
         kv_heads, dim = qk.shape[2], qk.shape[3]
         if qk.shape != (t, 2, kv_heads, dim) or out.shape != v.shape or state.shape[1:] != (heads, vdim, dim) \
@@ -1006,7 +1028,7 @@ class CudaKernels:
             raise KernelError("recurrent_scan: qk [tokens, 2, kv_heads, dim], v and out [tokens, heads, vdim], state "
                               "[slots, heads, vdim, dim], decay [tokens, heads, dim] or head_decay [heads], beta [tokens, heads]")
         self._call("hb_recurrent_scan", self._p(out), self._p(qk), self._p(v), self._p(decay), self._p(head_decay),
-                   self._p(token_decay), self._p(beta), self._p(state), self._i32(rows.query_start, "query_start"),
+                   self._p(token_decay), self._p(beta), self._p(rate), self._p(state), self._i32(rows.query_start, "query_start"),
                    self._i32(rows.row_slot, "row_slot"), rows.n_rows, heads, kv_heads, dim, vdim,
                    int(getattr(rows, "max_q", 0) or 0))
 
@@ -1050,8 +1072,26 @@ class CudaKernels:
                    self._i32(positions, "positions"), self._p(table), int(rot_dims),
                    table.shape[0] if table is not None else 0, t, heads, dim, vdim, ctypes.c_float(k_scale))
 
-    def head_norm_gate(self, out, o, weight, gate_mul, gate_pre, eps) -> None:
-        """out = o / rms(o) · weight · gate per head; `gate_pre` may be a view into wider rows (silu of it is the gate)."""
+    def gdelta_prepare(self, qk, v, decay, rate, first, pre, decay_bias, rate_bias, decay_scale, unit_eps) -> None:
+        """From the generalized delta rule's first product [tokens, r | k | v | g | a] and its low-rank decay projection's
+        output `pre` (float32 [tokens, heads dim]) to the scan's inputs (csrc/api.h: hb_gdelta_prepare)."""
+        self._check(qk, v, decay, rate, first, pre, decay_bias, rate_bias)
+        self._f32("gdelta_prepare", qk, v, decay, rate, pre, decay_bias, rate_bias)
+        t, heads, dim = v.shape
+        n = heads * dim
+        if qk.shape != (t, 2, heads, dim) or decay.shape != v.shape or rate.shape != v.shape or first.shape[0] != t \
+                or first.shape[1] < 5 * n or pre.shape != (t, n) or decay_bias.shape != (n,) or rate_bias.shape != (n,):
+            raise KernelError("gdelta_prepare: first [tokens, >= 5 heads dim], pre [tokens, heads dim], qk [tokens, 2, heads, "
+                              "dim], v, decay and rate [tokens, heads, dim], biases [heads dim]")
+        self._call("hb_gdelta_prepare", self._p(qk), self._p(v), self._p(decay), self._p(rate), self._p(first), _code(first),
+                   ctypes.c_long(first.shape[1]), self._p(pre), self._p(decay_bias), self._p(rate_bias), t, heads, dim,
+                   ctypes.c_float(decay_scale), ctypes.c_float(unit_eps))
+
+    def head_norm_gate(self, out, o, weight, gate_mul, gate_pre, eps, gate: str = "silu") -> None:
+        """out = o / rms(o) · weight · gate per head; `gate_pre` may be a view into wider rows (silu of it is the gate, or
+        with `gate="sigmoid"` its sigmoid); `weight` [vdim] for all heads or [heads vdim]."""
+        if gate not in ("silu", "sigmoid"):
+            raise KernelError(f"head_norm_gate: gate {gate!r}; known: silu, sigmoid")
         self._check(out, o, weight, gate_mul)
         self._f32("head_norm_gate", o, weight, gate_mul)
         t, heads, vdim = o.shape
@@ -1061,11 +1101,49 @@ class CudaKernels:
                     or gate_pre.get_device() != self._index:
                 raise KernelError("head_norm_gate: gate_pre must be [tokens, heads vdim] of out's dtype, innermost stride 1")
             ld = gate_pre.stride(0)
-        if out.shape != o.shape or (weight is not None and weight.shape != (vdim,)) \
+        per_head = weight is not None and heads > 1 and weight.shape == (heads * vdim,)
+        if out.shape != o.shape or (weight is not None and weight.shape != (vdim,) and not per_head) \
                 or (gate_mul is not None and gate_mul.numel() != o.numel()):
-            raise KernelError("head_norm_gate: out and o [tokens, heads, vdim], weight [vdim], gate_mul of o's size")
+            raise KernelError("head_norm_gate: out and o [tokens, heads, vdim], weight [vdim] or [heads vdim], gate_mul of o's size")
         self._call("hb_head_norm_gate", self._p(out), self._p(o), _code(out), self._p(weight), self._p(gate_mul),
-                   self._p(gate_pre), ctypes.c_long(ld), ctypes.c_float(eps), t, heads, vdim)
+                   self._p(gate_pre), ctypes.c_long(ld), ctypes.c_float(eps), t, heads, vdim, int(per_head),
+                   int(gate == "sigmoid"))
+
+    # ---- a norm without statistics and the blend with the token before (csrc/dyt.cu)
+    def dyt_add_norm(self, h, y, post, out, pre, index) -> None:
+        """With N(x) = tanh(alpha x) w + b for a triple (alpha, w, b) of float32 tensors: h (float32 [tokens, dim]) +=
+        N_post(y) (`post` None: y as it is; `y` None: nothing is added); out = N_pre of the sums, of all rows or of the
+        rows `index` (then h stays as it is). `h` None: out = N_pre(y), rows of any number of dimensions."""
+        tensors = [t for triple in (post, pre) if triple is not None for t in triple]
+        self._check(h, y, out, index, *tensors)
+        self._f32("dyt_add_norm", h, *tensors)
+        src = h if h is not None else y
+        dim = src.shape[-1]
+        rows = index.shape[0] if index is not None else src.numel() // dim
+        if (h is not None and y is not None and y.shape != h.shape) or (out is not None and (pre is None or out.numel() != rows * dim)) \
+                or any(t.numel() != dim for triple in (post, pre) if triple is not None for t in triple[1:]):
+            raise KernelError("dyt_add_norm: h and y [tokens, dim], out [rows, dim], weights and biases [dim]")
+        a, b = post or (None, None, None), pre or (None, None, None)
+        self._call("hb_dyt_add_norm", self._p(h), self._p(y), _code(y) if y is not None else 0, self._p(a[0]), self._p(a[1]),
+                   self._p(a[2]), self._p(out), _code(out) if out is not None else 0, self._p(b[0]), self._p(b[1]), self._p(b[2]),
+                   self._i32(index, "index"), rows, dim)
+
+    def dyt_shift(self, out, into, h, y, post, pre, mix, carried, rows) -> None:
+        """x = h + N_post(y) goes to `into` (h itself where y is None); n = N_pre(x); out_t = n_t + (n_(t-1) − n_t) · mix,
+        the first token of a row reading n_(t-1) from carried[slot] (float32 [slots, dim]), which then receives the row's
+        last n (csrc/api.h: hb_dyt_shift)."""
+        tensors = [t for triple in (post, pre) if triple is not None for t in triple]
+        self._check(out, into, h, y, mix, carried, rows.query_start, rows.row_slot, *tensors)
+        self._f32("dyt_shift", into, h, mix, carried, *tensors)
+        t, dim = h.shape
+        if out.shape != h.shape or into.shape != h.shape or (y is not None and (y.shape != h.shape or into is h)) \
+                or mix.shape != (dim,) or carried.shape[1:] != (dim,) or pre is None:
+            raise KernelError("dyt_shift: out, into, h, y [tokens, dim] (into apart from h with y), mix [dim], carried [slots, dim]")
+        a = post or (None, None, None)
+        self._call("hb_dyt_shift", self._p(out), _code(out), self._p(into), self._p(h), self._p(y),
+                   _code(y) if y is not None else 0, self._p(a[0]), self._p(a[1]), self._p(a[2]), self._p(pre[0]),
+                   self._p(pre[1]), self._p(pre[2]), self._p(mix), self._p(carried), self._i32(rows.query_start, "query_start"),
+                   self._i32(rows.row_slot, "row_slot"), rows.n_rows, t, dim)
 
     # ---- the matrix memory with exponential gates (csrc/mlstm.cu)
     def mlstm_gates(self, out, pre, bias, cap, m_state, rows) -> None:
