@@ -462,22 +462,49 @@ extern "C" int hb_expert_linear(void* out, const void* x, int dtype, const int32
 // act 4 (xielu, with two numbers p, q): softplus(p) v^2 + v / 2 for v > 0, (1/2 + softplus(q)) (exp(v) - 1 - v) + v / 2
 // otherwise; act 5: tanh. Both for this kernel alone (the experts' products know 1 to 3).
 __device__ __forceinline__ float softplus_e(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float any_act(float v, int act, float up, float down) {
+    if (act == 4) return v > 0.f ? fmaf(up * v, v, 0.5f * v) : fmaf(down, expm1f(v) - v, 0.5f * v);
+    if (act == 5) return tanhf(v);
+    return expert_act(v, act);
+}
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ x, long count, int act, const float* __restrict__ numbers) {
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
-    const float v = to_f32(x[i]);
-    float y;
-    if (act == 4) y = v > 0.f ? fmaf(softplus_e(numbers[0]) * v, v, 0.5f * v) : fmaf(0.5f + softplus_e(numbers[1]), expm1f(v) - v, 0.5f * v);
-    else if (act == 5) y = tanhf(v);
-    else y = expert_act(v, act);
-    x[i] = from_f32<T>(y);
+    const float up = act == 4 ? softplus_e(numbers[0]) : 0.f, down = act == 4 ? 0.5f + softplus_e(numbers[1]) : 0.f;
+    x[i] = from_f32<T>(any_act(to_f32(x[i]), act, up, down));
+}
+// The same, 16 bytes a thread (x on a 16-byte boundary; the few elements behind the last whole piece go one by one).
+template <typename T>
+__global__ void activation_wide_kernel(T* __restrict__ x, long count, int act, const float* __restrict__ numbers) {
+    constexpr int N = 16 / sizeof(T);
+    const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * N;
+    if (i >= count) return;
+    const float up = act == 4 ? softplus_e(numbers[0]) : 0.f, down = act == 4 ? 0.5f + softplus_e(numbers[1]) : 0.f;
+    if (i + N > count) {
+        for (long j = i; j < count; ++j) x[j] = from_f32<T>(any_act(to_f32(x[j]), act, up, down));
+        return;
+    }
+    uint4 v = *(const uint4*)(x + i);
+    T* e = (T*)&v;
+#pragma unroll
+    for (int j = 0; j < N; ++j) e[j] = from_f32<T>(any_act(to_f32(e[j]), act, up, down));
+    *(uint4*)(x + i) = v;
 }
 
 extern "C" int hb_activation(void* x, int dtype, long count, int act, const float* numbers, hb_stream stream) {
     if (count == 0) return 0;
     if (act == 4 && !numbers) HB_REFUSE("activation: xielu needs its two numbers");
     const unsigned blocks = (unsigned)((count + 255) / 256);
+    if (((uintptr_t)x & 15) == 0 && count >= 4096) {
+        const long per = dtype == HB_F32 ? 4 : 8;
+        const unsigned wide = (unsigned)(((count + per - 1) / per + 255) / 256);
+        if (dtype == HB_F32) activation_wide_kernel<float><<<wide, 256, 0, (cudaStream_t)stream>>>((float*)x, count, act, numbers);
+        else if (dtype == HB_BF16) activation_wide_kernel<bf16><<<wide, 256, 0, (cudaStream_t)stream>>>((bf16*)x, count, act, numbers);
+        else HB_REFUSE("activation: dtype %d", dtype);
+        HB_LAUNCH_CHECK("activation");
+        return 0;
+    }
     if (dtype == HB_F32) activation_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)x, count, act, numbers);
     else if (dtype == HB_BF16) activation_kernel<bf16><<<blocks, 256, 0, (cudaStream_t)stream>>>((bf16*)x, count, act, numbers);
     else HB_REFUSE("activation: dtype %d", dtype);

@@ -386,7 +386,8 @@ def layer(k, args) -> None:
 
 def scan(k, args) -> None:
     """The scan over a matrix state per head (`recurrent_scan`): one row of `--rows` tokens (1: eight rows of one token),
-    with the delta rule and a decay per key channel, and with one fixed decay per head."""
+    with the delta rule and a decay per key channel, with one fixed decay per head, and with removal rates per key channel
+    (the generalized delta rule)."""
     heads, kvh, dim, vdim = args.heads, args.kv_heads, args.dim, args.vdim
     dev = k.device
     for tokens in args.rows:
@@ -395,19 +396,21 @@ def scan(k, args) -> None:
         starts = torch.tensor([sum(counts[:i]) for i in range(len(counts) + 1)], dtype=torch.int32, device=dev)
         rows = Rows(torch.arange(len(counts), dtype=torch.int32, device=dev), starts, starts[1:].clone(), len(counts), t,
                     sum(1 for n in counts if n == 1), max(counts), max(counts))
-        for delta in (True, False):
+        for kind in ("delta rule", "fixed decay", "removal rates"):
+            delta, general = kind == "delta rule", kind == "removal rates"
             qk = torch.randn(t, 2, kvh if delta else heads, dim, device=dev) * 0.05
             v = torch.randn(t, heads, vdim, device=dev)
-            decay = torch.rand(t, heads, dim, device=dev) * 0.1 + 0.9 if delta else None
-            fixed = None if delta else torch.full((heads,), 0.99, device=dev)
+            decay = torch.rand(t, heads, dim, device=dev) * 0.1 + 0.9 if delta or general else None
+            fixed = None if delta or general else torch.full((heads,), 0.99, device=dev)
             beta = torch.rand(t, heads, device=dev) if delta else None
+            rate = torch.rand(t, heads, dim, device=dev) if general else None
             state = torch.zeros(len(counts), heads, vdim, dim, device=dev)
             out = torch.empty(t, heads, vdim, device=dev)
-            us = timed(lambda: k.recurrent_scan(out, qk, v, decay, fixed, beta, state, rows), None)
-            moved = 2 * state.numel() * 4 + (qk.numel() + 2 * v.numel() + (decay.numel() if delta else 0)) * 4
+            us = timed(lambda: k.recurrent_scan(out, qk, v, decay, fixed, beta, state, rows, rate=rate), None)
+            moved = 2 * state.numel() * 4 + (qk.numel() + 2 * v.numel() + (decay.numel() if decay is not None else 0)
+                                             + (rate.numel() if general else 0)) * 4
             print(f"scan {len(counts)} row(s) of {counts[0]:5d} tokens, {heads} heads of {dim} x {vdim}, "
-                  f"{'delta rule' if delta else 'fixed decay'}: {us:8.1f} us  ({us / counts[0]:6.3f} us a token, "
-                  f"{moved / 1e6:6.1f} MB moved)")
+                  f"{kind}: {us:8.1f} us  ({us / counts[0]:6.3f} us a token, {moved / 1e6:6.1f} MB moved)")
 
 
 def main() -> None:

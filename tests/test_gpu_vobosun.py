@@ -140,7 +140,7 @@ def _delta_inputs(t, heads, dim, seed, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,dim", [(2, 16), (1, 20), (2, 96), (3, 8), (1, 4), (2, 128), (1, 300)])
+@pytest.mark.parametrize("heads,dim", [(2, 16), (1, 20), (2, 96), (3, 8), (1, 4), (2, 128), (1, 300), (2, 10), (1, 7)])
 def test_delta_rows_in_slots_and_in_portions(K, dtype, heads, dim):
     """The prepare kernel against the written-out rule, and the scan with removal rates against its twin: rows of 1, 37,
     1 and 6 tokens in slots 3, 0, 2, 5 on states that are not zero, then the same tokens again as one-token rows and as
@@ -402,6 +402,29 @@ def test_far_keys_through_the_model(tmp_path, dtype):
     compare(run(r, [([("r", ids)], ["r"])]), want, dtype)
     steps = [([("r", ids[:180])], [])] + [([("r", [t])], ["r"] if i == 119 else []) for i, t in enumerate(ids[180:])]
     compare(run(r, steps), want, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("vdim", [128, 64])
+def test_heads_of_128(tmp_path, dtype, vdim):
+    """Attention heads of 128 (the tcgen05 prompt kernel and the cluster decode kernel in bfloat16 where keys and values
+    are of one size; rows [key | value] where they are not), a delta head of 64 and one of 128, 300 tokens: whole, the
+    last 40 tokens one by one, and portions that end inside pages."""
+    from vobosun_tools import _att, _delta, _dense, _layer, _model, _moe
+    config = _model(256, 331, 1e-6, [
+        _layer("attention", _att(4, 2, 128, vdim, 6.0, 500000.0, 64, 2.0), _moe(6, 2, 64, identity=2, groups=(4, 2), shared=32)),
+        _layer("general_delta", _delta(2, 64, 8), _dense(192)),
+        _layer("attention", _att(4, 2, 128, vdim, 6.0, 500000.0, 64, 2.0), _dense(192), weights_of=None),
+        _layer("general_delta", _delta(1, 128, 12), None)])
+    folder = make_folder(tmp_path, "wide", seed=9, config=config)
+    ids = random_prompt(config["vocab"], 300, 4)
+    want = {"r": exact_logits(folder, ids)}
+    r = Replayer(str(folder), dtype, 320, device=DEV, page_size=64)
+    compare(run(r, [([("r", ids)], ["r"])]), want, dtype)
+    steps = [([("r", ids[:260])], [])] + [([("r", [t])], ["r"] if i == 39 else []) for i, t in enumerate(ids[260:])]
+    compare(run(r, steps), want, dtype)
+    parts = portions(ids, [100, 3, 61, 2, 90])
+    compare(run(r, [([("r", p)], ["r"] if i == len(parts) - 1 else []) for i, p in enumerate(parts)]), want, dtype)
 
 
 def test_a_token_far_back_is_remembered(tmp_path):
