@@ -146,7 +146,7 @@ def vobosun_config(width: int, heads: int, kv_heads: int, dim: int, ff: int, exp
     attention with biases and a stretched rotation; odd layers have routed gated experts in groups (with identity experts
     and a shared one), even layers a dense xielu feed-forward; every layer blends its mixer's input with the token before."""
     attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                 "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 2.0}}}
+                 "rot": {"base": 1000000.0, "dims": dim, "scaling": {"factor": 8.0}}}
     delta = {"heads": delta_heads, "dim": delta_dim, "decay_rank": rank}
     moe = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}},
            "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}

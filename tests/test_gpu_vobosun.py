@@ -412,9 +412,9 @@ def test_heads_of_128(tmp_path, dtype, vdim):
     last 40 tokens one by one, and portions that end inside pages."""
     from vobosun_tools import _att, _delta, _dense, _layer, _model, _moe
     config = _model(256, 331, 1e-6, [
-        _layer("attention", _att(4, 2, 128, vdim, 6.0, 500000.0, 64, 2.0), _moe(6, 2, 64, identity=2, groups=(4, 2), shared=32)),
+        _layer("attention", _att(4, 2, 128, vdim, 6.0, 1000000.0, 64, 4.0), _moe(6, 2, 64, identity=2, groups=(4, 2), shared=32)),
         _layer("general_delta", _delta(2, 64, 8), _dense(192)),
-        _layer("attention", _att(4, 2, 128, vdim, 6.0, 500000.0, 64, 2.0), _dense(192), weights_of=None),
+        _layer("attention", _att(4, 2, 128, vdim, 6.0, 1000000.0, 64, 4.0), _dense(192), weights_of=None),
         _layer("general_delta", _delta(1, 128, 12), None)])
     folder = make_folder(tmp_path, "wide", seed=9, config=config)
     ids = random_prompt(config["vocab"], 300, 4)

@@ -255,3 +255,128 @@ def test_greedy_generation_through_the_scheduler(model):
             second = float(logits.topk(2).values[1])
             assert token == best or float(logits[best]) - second < 1e-3, (len(ids), token, best)
             ids.append(token)
+
+
+# ---------------------------------------------------------------- faults planted in the kernel table are noticed
+class _Planted(RefKernels):
+    """The plain kernel table with one fault; `fault` names it."""
+
+    def __init__(self, fault: str) -> None:
+        self.fault = fault
+
+    def dyt_shift(self, out, into, h, y, post, pre, mix, carried, rows):
+        if self.fault == "the previous row is not carried from step to step":
+            kept = carried.clone()
+            super().dyt_shift(out, into, h, y, post, pre, mix, carried, rows)
+            carried.copy_(kept)
+            return
+        if self.fault == "a row's first token blends with the row before it in the batch":
+            super().dyt_shift(out, into, h, y, post, pre, mix, carried, rows)
+            qs = rows.query_start.tolist()
+            n = self._dyt(into, pre)
+            for b in range(1, rows.n_rows):
+                s = qs[b]
+                if qs[b + 1] > s:
+                    out[s] = (n[s] + (n[s - 1] - n[s]) * mix.float()).to(out.dtype)
+            return
+        super().dyt_shift(out, into, h, y, post, pre, mix, carried, rows)
+
+    def recurrent_scan(self, out, qk, v, decay, head_decay, beta, state, rows, token_decay=None, rate=None):
+        if rate is not None and self.fault == "the removal reads the decayed state":
+            qs, slots = rows.query_start.tolist(), rows.row_slot.tolist()
+            for b in range(rows.n_rows):
+                for h in range(v.shape[1]):
+                    s = state[slots[b], h].T.clone()
+                    for i in range(qs[b], qs[b + 1]):
+                        k = qk[i, 1, h]
+                        s = s * decay[i, h][:, None]
+                        s = s + torch.outer(k, v[i, h]) - torch.outer(rate[i, h] * k, s.T @ k)
+                        out[i, h] = s.T @ qk[i, 0, h]
+                    state[slots[b], h] = s.T
+            return
+        if rate is not None and self.fault == "the state is not written back":
+            kept = state.clone()
+            super().recurrent_scan(out, qk, v, decay, head_decay, beta, state, rows, token_decay, rate)
+            state.copy_(kept)
+            return
+        super().recurrent_scan(out, qk, v, decay, head_decay, beta, state, rows, token_decay, rate)
+
+    def gdelta_prepare(self, qk, v, decay, rate, first, pre, decay_bias, rate_bias, decay_scale, unit_eps):
+        super().gdelta_prepare(qk, v, decay, rate, first, pre, decay_bias, rate_bias, decay_scale, unit_eps)
+        if self.fault == "the removal runs along the key, not the unit key":
+            k = qk[:, 1]
+            rate.mul_((k * k).sum(-1, keepdim=True) + unit_eps)
+
+    def route_rows(self, chosen, weight, counts, place, token_of, z, experts, scale, renormalize, bias=None,
+                   correction=None, groups=1, keep=1, tiny=0.0):
+        if self.fault == "the choice runs without the correction":
+            correction = None
+        if self.fault == "the groups are ignored":
+            groups, keep = 1, 1
+        super().route_rows(chosen, weight, counts, place, token_of, z, experts, scale, renormalize, bias, correction, groups, keep, tiny)
+
+    def expert_combine(self, out, y, place, weight, shared, z, experts, x=None, identity_from=None):
+        if self.fault == "identity experts return nothing" and x is not None:
+            x = torch.zeros_like(x)
+        if self.fault == "the shared expert is left out":
+            shared = None
+        super().expert_combine(out, y, place, weight, shared, z, experts, x, identity_from)
+
+    def qk_norm_rope_kv_write(self, *args, bias=None):
+        if self.fault == "q, k and v lose their biases":
+            bias = None
+        super().qk_norm_rope_kv_write(*args, bias=bias)
+
+    def activation(self, x, act, numbers=None):
+        if self.fault == "xielu's two numbers are swapped" and numbers is not None:
+            numbers = numbers.flip(0)
+        super().activation(x, act, numbers)
+
+    def head_norm_gate(self, out, o, weight, gate_mul, gate_pre, eps, gate="silu"):
+        if self.fault == "the output gate is silu":
+            gate = "silu"
+        super().head_norm_gate(out, o, weight, gate_mul, gate_pre, eps, gate=gate)
+
+
+FAULTS = ("the previous row is not carried from step to step", "a row's first token blends with the row before it in the batch",
+          "the removal reads the decayed state", "the state is not written back", "the removal runs along the key, not the unit key",
+          "the choice runs without the correction", "the groups are ignored", "identity experts return nothing",
+          "the shared expert is left out", "q, k and v lose their biases", "xielu's two numbers are swapped",
+          "the output gate is silu")
+
+
+def test_planted_faults_are_noticed(tmp_path):
+    """Portions beside single tokens of three requests of configuration `a`, in 32-bit: the comparison accepts the plain
+    kernel table and rejects every table with one fault planted (a rotation whose stretch is ignored is planted in the
+    configuration)."""
+    folder = make_folder(tmp_path, "a", seed=7)
+    config = CONFIGS["a"]
+    prompts = {f"r{i}": random_prompt(config["vocab"], n, 60 + i) for i, n in enumerate((23, 41, 30))}
+    want = {rid: exact_logits(folder, ids) for rid, ids in prompts.items()}
+    cut = {rid: portions(ids, sizes) for (rid, ids), sizes in zip(prompts.items(), ([5, 1, 1, 3], [2, 9, 1], [30]))}
+    steps = []
+    for j in range(max(len(p) for p in cut.values())):
+        steps.append(([(rid, p[j]) for rid, p in cut.items() if j < len(p)], [rid for rid, p in cut.items() if j == len(p) - 1]))
+
+    def replay(where, kernels):
+        return run(Replayer(str(where), "float32", 128, device="cpu", kernels=kernels, page_size=4), steps)
+
+    compare(replay(folder, RefKernels()), want, "float32")
+    missed = []
+    for fault in FAULTS:
+        try:
+            compare(replay(folder, _Planted(fault)), want, "float32")
+            missed.append(fault)
+        except AssertionError:
+            pass
+    stored, weights = read_folder(folder)
+    for layer in stored["layers"]:
+        if layer["type"] == "attention" and "scaling" in layer["mixer"].get("rot", {}):
+            layer["mixer"]["rot"]["scaling"]["factor"] = 1.0
+    other = make_folder(tmp_path / "unstretched", "a", config=stored, weights=weights)
+    try:
+        compare(replay(other, RefKernels()), want, "float32")
+        missed.append("the rotation's stretch is ignored")
+    except AssertionError:
+        pass
+    assert not missed, f"the comparison accepted: {missed}"
