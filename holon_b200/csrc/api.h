@@ -242,6 +242,11 @@ int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void* w, int m, 
                               int weight_f32, float eps, float offset, void* kv, const int32_t* write_index, int pages,
                               int page_size, int heads, int kv_heads, int head_dim, const float* ss_in, int parts_in,
                               float eps_in, int dim_in, hb_stream stream);
+// The same link for a norm without statistics, N(y) = tanh(alpha y) weight + bias (alpha one number on the device, weights
+// and biases float32 [n]): h [m, n] (float32) += N_post(bfloat16(x · wᵀ)); out (bfloat16 [m, n], or null) = N_pre(h).
+int hb_gemm_bf16_skinny_dyt(void* out, const void* x, const void* w, int m, int n, int k, float* h, const float* post_alpha,
+                            const float* post_w, const float* post_b, const float* pre_alpha, const float* pre_w,
+                            const float* pre_b, hb_stream stream);
 // The same two for up to 32 rows (four 8-row tiles of x a warp; meant for 17 to 32 rows and weights of a few MB, where a
 // product is its launch): ss_in and ss_out hold 32 tokens a part.
 int hb_gemm_bf16_skinny32(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,

@@ -17,6 +17,8 @@
 // mode 3 folds the residual sum and the next RMSNorm into a product that ends a mixer or a feed-forward: the CTA adds
 // its 16 columns (rounded to bfloat16, as the separate product's output is) into the 32-bit stream h, writes the new
 // stream times the next norm's weight as bfloat16, and leaves the sum of squares of its columns per token. The
+// (mode 4 is the same link for a norm without statistics, N(y) = tanh(alpha y) w + b: h += N_post(bfloat16(x · wᵀ)) and,
+// where an output is given, out = N_pre(h); nothing is left for the next product to scale.)
 // product that consumes those rows (any mode, `NormLink::ss_in`) adds the partial sums up in a fixed order and scales
 // its sums by rsqrt(mean + eps) per token: x · rstd · w == (x · w) · rstd, so the norm costs no kernel and no pass
 // over the stream of its own.
@@ -48,6 +50,8 @@ struct NormLink {                                  // the residual stream and th
     float next_offset, eps_in;
     int next_weight_f32, parts_in, dim_in;
     int stride_in, stride_out;                     // tokens a part of ss_in / ss_out holds (16, or 32 for the 32-row kernels)
+    const float* post[3];                          // mode 4: alpha (one number), weight [n], bias [n] of the norm the product passes
+    const float* pre[3];                           // mode 4: the same of the norm of the new stream (with an output)
 };
 
 __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
@@ -295,6 +299,24 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
         }
         return;
     }
+    if (MT == 1 && mode == 4) {                                      // as mode 3, for the norm without statistics
+        const int rr = threadIdx.x & 15, col = row0[0] + rr;
+        if (col >= n) return;
+        const float pa = *link.post[0], pw = link.post[1][col], pb = link.post[2][col];
+        const float na = out ? *link.pre[0] : 0.f, nw = out ? link.pre[1][col] : 0.f, nb = out ? link.pre[2][col] : 0.f;
+#pragma unroll
+        for (int tok = threadIdx.x >> 4; tok < TOKP; tok += 16) {
+            if (tok >= m) continue;
+            float v = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
+            const float y = rounded<bf16>(v * scale_in[tok]);
+            const float hn = link.h[(size_t)tok * n + col] + fmaf(tanhf(pa * y), pw, pb);
+            link.h[(size_t)tok * n + col] = hn;
+            if (out) ((bf16*)out)[(size_t)tok * n + col] = __float2bfloat16_rn(fmaf(tanhf(na * hn), nw, nb));
+        }
+        return;
+    }
     const int rows_out = mode == 1 ? HALF * 16 : MT * 16;
     const int width = mode == 1 ? inter : n;
     for (int i = threadIdx.x; i < rows_out * m; i += SK_WARPS * 32) {
@@ -327,18 +349,22 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
 // m at most 16, k a multiple of 8, all pointers 16-byte aligned.
 static int skinny_product(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
                           float* h, const void* next_weight, int next_weight_f32, float next_offset, float* ss_out,
-                          const float* ss_in, int parts_in, float eps_in, int dim_in, int most, hb_stream stream) {
+                          const float* ss_in, int parts_in, float eps_in, int dim_in, int most, hb_stream stream,
+                          const float* const* post = nullptr, const float* const* pre = nullptr) {
     if (m == 0) return 0;
     if (m < 0 || m > most) HB_REFUSE("gemm_bf16_skinny: %d rows; this kernel takes 1 to %d", m, most);
     if (k < 8 || k % 8) HB_REFUSE("gemm_bf16_skinny: k = %d is no multiple of 8", k);
     if ((((uintptr_t)out | (uintptr_t)x | (uintptr_t)w) % 16) != 0) HB_REFUSE("gemm_bf16_skinny: pointers must be 16-byte aligned");
-    if (mode != 0 && mode != 1 && mode != 3) HB_REFUSE("gemm_bf16_skinny: mode %d", mode);
+    if (mode != 0 && mode != 1 && mode != 3 && mode != 4) HB_REFUSE("gemm_bf16_skinny: mode %d", mode);
+    if (mode == 4 && (!h || !post || !post[0] || !post[1] || !post[2] || out_f32 || (out && (!pre || !pre[0] || !pre[1] || !pre[2]))))
+        HB_REFUSE("gemm_bf16_skinny: mode 4 needs h and the norm the product passes, with an output also the norm of the new stream, and writes bfloat16");
     if (mode == 3 && (!h || !next_weight || !ss_out || out_f32)) HB_REFUSE("gemm_bf16_skinny: mode 3 needs h, the next norm's weight and ss_out, and writes bfloat16");
     if (ss_in && (parts_in < 1 || dim_in < 1)) HB_REFUSE("gemm_bf16_skinny: %d partial sums over %d columns", parts_in, dim_in);
     NormLink link = {};
     link.h = h; link.next_weight = next_weight; link.ss_out = ss_out; link.ss_in = ss_in; link.next_offset = next_offset;
     link.eps_in = eps_in; link.next_weight_f32 = next_weight_f32; link.parts_in = parts_in; link.dim_in = dim_in;
     link.stride_in = link.stride_out = most;             // (16 tokens a part, or 32: both sides of a link run the same kernels)
+    for (int i = 0; i < 3; ++i) { link.post[i] = post ? post[i] : nullptr; link.pre[i] = pre && out ? pre[i] : nullptr; }
     cudaStream_t s = (cudaStream_t)stream;
     static int sms = 0;
     if (sms == 0) {
@@ -395,8 +421,19 @@ extern "C" int hb_gemm_bf16_skinny32(void* out, int out_f32, const void* x, cons
                           ss_in, parts_in, eps_in, dim_in, 32, stream);
 }
 
+// h [m, n] (float32) += N_post(bfloat16(x · wᵀ)) with N(y) = tanh(alpha y) weight + bias (alpha one number on the device,
+// weights and biases float32 [n]); out (bfloat16 [m, n], or null) = N_pre of the new h. m at most 16.
+extern "C" int hb_gemm_bf16_skinny_dyt(void* out, const void* x, const void* w, int m, int n, int k, float* h,
+                                       const float* post_alpha, const float* post_w, const float* post_b,
+                                       const float* pre_alpha, const float* pre_w, const float* pre_b, hb_stream stream) {
+    const float* post[3] = {post_alpha, post_w, post_b};
+    const float* pre[3] = {pre_alpha, pre_w, pre_b};
+    return skinny_product(out, 0, x, w, m, n, k, 4, 0, h, nullptr, 0, 0.f, nullptr, nullptr, 0, 0.f, 0, 16, stream, post, pre);
+}
+
 extern "C" int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode,
                                    int inter, hb_stream stream) {
+    if (mode == 4) HB_REFUSE("gemm_bf16_skinny: mode 4 goes through hb_gemm_bf16_skinny_dyt");
     if (mode == 3) HB_REFUSE("gemm_bf16_skinny: mode 3 goes through hb_gemm_bf16_skinny_linked");
     return hb_gemm_bf16_skinny_linked(out, out_f32, x, w, m, n, k, mode, inter, nullptr, nullptr, 0, 0.f, nullptr, nullptr,
                                       0, 0.f, 0, stream);

@@ -621,6 +621,28 @@ class CudaKernels:
                    None, 0, ctypes.c_float(0.0), 0)
         return Scaled(y, ss, float(eps), n)
 
+    def linear_dyt(self, h, x, weight, post, pre):
+        """h [m, n] (float32) += N_post(bfloat16(x · weightᵀ)) with N(y) = tanh(alpha y) w + b for a triple (alpha, w, b) of
+        float32 tensors, in the epilogue of the product for the few rows of a decode step; returns N_pre of the new h
+        (bfloat16 [m, n]; `pre` None: True). None, with nothing done, where the kernel does not apply (another dtype, k
+        no multiple of 8, more than SKINNY_ROWS rows)."""
+        m, k = x.shape
+        n = weight.shape[0]
+        if not self.fused_norm or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or h.dtype != torch.float32 \
+                or k % 8 or not 0 < m <= self.SKINNY_ROWS or tuple(h.shape) != (m, n) or weight.shape != (n, k) \
+                or (x.data_ptr() | weight.data_ptr()) % 16 or not x.is_contiguous():
+            return None
+        tensors = [t for triple in (post, pre) if triple is not None for t in triple]
+        self._check(h, x, weight, *tensors)
+        self._f32("linear_dyt", *tensors)
+        if any(t.numel() != n for triple in (post, pre) if triple is not None for t in triple[1:]):
+            raise KernelError("linear_dyt: the norms' weights and biases must be [n]")
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device) if pre is not None else None
+        b = pre or (None, None, None)
+        self._call("hb_gemm_bf16_skinny_dyt", self._p(out), self._p(x), self._p(weight), m, n, k, self._p(h), self._p(post[0]),
+                   self._p(post[1]), self._p(post[2]), self._p(b[0]), self._p(b[1]), self._p(b[2]))
+        return out if out is not None else True
+
     def _scaled_product(self, out, x, weight, mode: int, inter: int) -> None:
         """A product whose x is parts.base.Scaled: the weight-streaming kernel applies the row scale to its sums."""
         y = x.y

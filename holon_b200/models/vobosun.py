@@ -148,7 +148,7 @@ class VobosunConfig:
                     router = _get(mlp, "router", Mapping, wf)
                     groups, shared = router.get("groups"), mlp.get("shared")
                     listed_all = _get(router, "experts", int, wf + ".router")
-                    identity = _get(router, "identity", int, wf + ".router") if "identity" in router else 0
+                    identity = _get(router, "identity", int, wf + ".router") if router.get("identity") is not None else 0
                     unit = ExpertUnits(
                         experts=listed_all, identity=identity, top=_get(router, "top", int, wf + ".router"),
                         groups=_get(groups, "count", int, wf + ".router.groups") if groups is not None else 1,

@@ -215,10 +215,11 @@ class Link:
     the rows of `norm` behind (`Linear.forward(x, link=...)`). A part that takes it from `step.link` returns None in
     place of its output; a part that knows nothing of it returns its output as ever."""
 
-    __slots__ = ("stream", "norm")
+    __slots__ = ("stream", "norm", "post")
 
-    def __init__(self, stream: Residual, norm) -> None:
+    def __init__(self, stream: Residual, norm, post=None) -> None:
         self.stream, self.norm = stream, norm
+        self.post = post                     # a norm the product's output passes before it is added (a sandwich block's)
 
 
 def take_link(step):

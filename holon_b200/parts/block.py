@@ -154,11 +154,18 @@ class Sandwich(Part):
             x = self.mixer_norm.add_shifted(stream, self.shift.tensor, cache.slots["block.shift"], step.rows)
         else:
             x = self.mixer_norm.add(stream)
-        step.link = None
+        # for the few rows of a decode step the product that ends the mixer may add its normed output and norm the sum
+        # for the feed-forward in its epilogue (base.Link with `post`): it then returns None and leaves the rows behind
+        step.link = Link(stream, self.ffn_norm, post=self.mixer_out_norm) \
+            if self.ffn is not None and hasattr(self.mixer_out_norm, "triple") and hasattr(self.ffn_norm, "triple") else None
         y = self.mixer.forward(x, step, cache)
+        step.link = None
         if self.ffn is None:
             stream.delta, stream.delta_by = y, self.mixer_out_norm
             return stream
-        x = self.mixer_out_norm.add_then(stream, y, self.ffn_norm)
+        if y is None:
+            x, stream.normed, stream.normed_by = stream.normed, None, None
+        else:
+            x = self.mixer_out_norm.add_then(stream, y, self.ffn_norm)
         stream.delta, stream.delta_by = self.ffn.forward(x, step), self.ffn_out_norm
         return stream

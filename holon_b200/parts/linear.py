@@ -23,7 +23,13 @@ class Linear(Part):
         """x · Wᵀ. With `link` (base.Link): the product is added into the link's stream, the rows of the link's norm
         are left on the stream, and None is returned; where the kernel table has no such product for these sizes, the
         plain product is returned as ever."""
-        if link is not None:
+        if link is not None and getattr(link, "post", None) is not None:        # the output passes a norm of its own first
+            fused = getattr(self.ctx.kernels, "linear_dyt", None)
+            rows = fused(link.stream.h, x, self.weight.tensor, link.post.triple(), link.norm.triple()) if fused else None
+            if rows is not None:
+                link.stream.normed, link.stream.normed_by = rows, link.norm
+                return None
+        elif link is not None:
             stream, norm = link.stream, link.norm
             rows = self.ctx.kernels.linear_link(stream.h, x, self.weight.tensor, norm.weight.tensor, norm.eps, norm.offset)
             if rows is not None:                           # (None: that kernel does not take these sizes or this dtype)

@@ -40,7 +40,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import PartRef
-from .base import BuildContext, Part, SlotState
+from .base import BuildContext, Part, SlotState, take_link
 from .linear import Linear
 
 ACT_TANH = 5                          # the kernel table's activation code (parts/experts.py: ACTIVATIONS)
@@ -235,4 +235,4 @@ class GeneralDelta(_MatrixState):
         k.recurrent_scan(o, qk, v, decay, None, None, cache.slots["state"], step.rows, rate=rate)
         y = ctx.empty(t, heads, dim)
         k.head_norm_gate(y, o, self.gain.tensor, None, first[:, 3 * n:4 * n], self.eps, gate="sigmoid")
-        return self.out.forward(y.view(t, n))
+        return self.out.forward(y.view(t, n), link=take_link(step))

@@ -131,6 +131,31 @@ def test_rows_blended_with_the_token_before(K, dtype, dim, pending):
         carried = cg.cpu()
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (8, 256, 128), (16, 72, 200), (5, 2048, 512), (17, 64, 64), (3, 64, 60)])
+@pytest.mark.parametrize("with_out", [True, False])
+def test_the_sum_and_norm_in_a_product_s_epilogue(K, m, n, k, with_out):
+    """For the few rows of a decode step: h += N_post(x · Wᵀ), out = N_pre(h) inside the product, against the product
+    followed by the kernel of its own; more than 16 rows and a k that is no multiple of 8 are left to those two."""
+    x, w = rand(m, k, dtype=torch.bfloat16, seed=1), rand(n, k, dtype=torch.bfloat16, seed=2, scale=k ** -0.5)
+    h, post, pre = rand(m, n, seed=3, scale=2.0), triple(n, 1), triple(n, 3)
+    hg = h.to(DEV)
+    got = K.linear_dyt(hg, x.to(DEV), w.to(DEV), gpu(post), gpu(pre) if with_out else None)
+    if m > 16 or k % 8:
+        assert got is None and torch.equal(hg.cpu(), h)
+        return
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    K.linear(y, x.to(DEV), w.to(DEV))
+    h2, out2 = h.to(DEV), torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    K.dyt_add_norm(h2, y, gpu(post), out2 if with_out else None, gpu(pre) if with_out else None, None)
+    close(hg, h2, torch.float32, 4.0)
+    if with_out:
+        close(got, out2, torch.bfloat16, 2.0)
+    else:
+        assert got is True
+    y64 = (x.to(F64) @ w.to(F64).T).to(torch.bfloat16).to(F64)
+    close(hg, h.to(F64) + torch.tanh(post[0].to(F64) * y64) * post[1].to(F64) + post[2].to(F64), torch.bfloat16, 1.0)
+
+
 # ---------------------------------------------------------------- the generalized delta rule
 def _delta_inputs(t, heads, dim, seed, dtype):
     n = heads * dim
