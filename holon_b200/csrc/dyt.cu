@@ -4,7 +4,8 @@
 // hb_dyt_add_norm   h += N_post(y);  out = N_pre(h)          (either half may be left out; rows may be gathered)
 // hb_dyt_shift      x_t = h_t + N_post(y_t);  n_t = N_pre(x_t);  out_t = n_t + (n_(t-1) - n_t) mix
 //                   with n_(t-1) of a row's first token carried per request slot, and the row's last n written there
-// Nothing here sums over a row, so the grid is flat: a thread four neighbouring columns of one token. 32-bit arithmetic,
+// Nothing here sums over a row, so the grid is flat: a thread four neighbouring columns of one token (in the blend
+// kernel, for prompts, of four tokens one after the other). 32-bit arithmetic,
 // one rounding where the output is stored.
 #include "common.cuh"
 
@@ -122,19 +123,19 @@ __device__ __forceinline__ int dyt_row_of_token(const int32_t* __restrict__ quer
     return lo;
 }
 
-// grid (tokens, column segments). The thread of a row's first token reads what the slot carries and then, alone, writes
-// the row's last normed row there (which it computes itself): no other thread touches those four numbers.
+// grid (groups of `walk` tokens, column segments): a thread walks the tokens of its group for its four columns and keeps
+// the normed row it made for the next token (the group's first token recomputes the row before it, unless it is a row's
+// first). The thread that meets a row's first token reads what the slot carries and then, alone, writes the row's last
+// normed row there (which it computes itself): no other thread touches those four numbers.
 template <typename TY, typename TO>
 __global__ void dyt_shift_kernel(TO* __restrict__ out, float* __restrict__ into, const float* __restrict__ h,
                                  const TY* __restrict__ y, DytNorm post, DytNorm pre, const float* __restrict__ mix,
                                  float* __restrict__ carried, const int32_t* __restrict__ query_start,
-                                 const int32_t* __restrict__ row_slot, int rows, int dim, int vec) {
-    const int t = blockIdx.x;
+                                 const int32_t* __restrict__ row_slot, int rows, int tokens, int dim, int vec, int walk) {
+    const int first_token = blockIdx.x * walk, end = min(tokens, first_token + walk);
     const int d = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (d >= dim) return;
     const int left = dim - d;
-    const int b = dyt_row_of_token(query_start, rows, t);
-    const int t0 = query_start[b], t1 = query_start[b + 1];
     float wq[4], bq[4], wp[4], bp[4], mu[4];
     const float ap = *pre.alpha, aq = post.alpha ? *post.alpha : 0.f;
     load4<float>(pre.w + d, vec, left, wp);
@@ -150,31 +151,40 @@ __global__ void dyt_shift_kernel(TO* __restrict__ out, float* __restrict__ into,
             for (int i = 0; i < 4; ++i) x[i] += post.alpha ? dyt_one(z[i], aq, wq[i], bq[i]) : z[i];
         }
     };
-    float x[4], n[4], before[4];
-    summed(t, x);
-    if (y || into != h) store4(into + (size_t)t * dim + d, vec, left, x);
+    int b = dyt_row_of_token(query_start, rows, first_token);
+    float before[4];
+    bool have = false;                                               // `before` holds the normed row of token t - 1
+    for (int t = first_token; t < end; ++t) {
+        while (t >= query_start[b + 1]) ++b;                         // (rows without tokens are passed over)
+        const int t0 = query_start[b], t1 = query_start[b + 1];
+        float x[4], n[4];
+        summed(t, x);
+        if (y || into != h) store4(into + (size_t)t * dim + d, vec, left, x);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) n[i] = dyt_one(x[i], ap, wp[i], bp[i]);
-    float* kept = carried + (size_t)row_slot[b] * dim + d;
-    if (t == t0) {
-        load4<float>(kept, vec, left, before);
-        if (t1 - 1 == t) {
-            store4(kept, vec, left, n);
-        } else {
-            float xl[4];
-            summed(t1 - 1, xl);
+        for (int i = 0; i < 4; ++i) n[i] = dyt_one(x[i], ap, wp[i], bp[i]);
+        if (t == t0) {
+            float* kept = carried + (size_t)row_slot[b] * dim + d;
+            load4<float>(kept, vec, left, before);
+            if (t1 - 1 == t) {
+                store4(kept, vec, left, n);
+            } else {
+                float xl[4];
+                summed(t1 - 1, xl);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) xl[i] = dyt_one(xl[i], ap, wp[i], bp[i]);
-            store4(kept, vec, left, xl);
+                for (int i = 0; i < 4; ++i) xl[i] = dyt_one(xl[i], ap, wp[i], bp[i]);
+                store4(kept, vec, left, xl);
+            }
+        } else if (!have) {
+            summed(t - 1, before);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) before[i] = dyt_one(before[i], ap, wp[i], bp[i]);
         }
-    } else {
-        summed(t - 1, before);
+        float o[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) before[i] = dyt_one(before[i], ap, wp[i], bp[i]);
+        for (int i = 0; i < 4; ++i) { o[i] = fmaf(before[i] - n[i], mu[i], n[i]); before[i] = n[i]; }
+        have = true;
+        store4(out + (size_t)t * dim + d, vec, left, o);
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) n[i] = fmaf(before[i] - n[i], mu[i], n[i]);
-    store4(out + (size_t)t * dim + d, vec, left, n);
 }
 
 extern "C" int hb_dyt_shift(void* out, int out_dtype, float* into, const float* h, const void* y, int y_dtype,
@@ -189,11 +199,12 @@ extern "C" int hb_dyt_shift(void* out, int out_dtype, float* into, const float* 
                                       (uintptr_t)post_b | (uintptr_t)pre_w | (uintptr_t)pre_b | (uintptr_t)mix |
                                       (uintptr_t)carried) & 15) == 0;
     const int quads = (dim + 3) / 4, threads = quads >= 256 ? 256 : ((quads + 31) / 32) * 32;
-    const dim3 grid(tokens, (quads + threads - 1) / threads);
+    const int walk = tokens >= 1024 ? 4 : 1;            // prompts: a thread four tokens; the few rows of a decode step: one each
+    const dim3 grid((tokens + walk - 1) / walk, (quads + threads - 1) / threads);
     const DytNorm post{post_alpha, post_w, post_b}, pre{pre_alpha, pre_w, pre_b};
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_RUN(TY, TO) dyt_shift_kernel<TY, TO><<<grid, threads, 0, s>>>((TO*)out, into, h, (const TY*)y, post, pre, mix, carried, \
-                                                                         query_start, row_slot, rows, dim, vec)
+                                                                         query_start, row_slot, rows, tokens, dim, vec, walk)
     if (y_dtype == HB_F32 && out_dtype == HB_F32) HB_RUN(float, float);
     else if (y_dtype == HB_BF16 && out_dtype == HB_BF16) HB_RUN(bf16, bf16);
     else if (y_dtype == HB_F32 && out_dtype == HB_BF16) HB_RUN(float, bf16);

@@ -97,11 +97,13 @@ def test_tanh_norm_with_sum_and_gather(K, dtype, rows, dim):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("dim", [64, 72, 1030, 33])
 @pytest.mark.parametrize("pending", [False, True])
-def test_rows_blended_with_the_token_before(K, dtype, dim, pending):
-    """Rows of 1, 5, 1 and 2 tokens in slots 3, 0, 2, 5: a row's first token reads what its slot carries, later tokens
+@pytest.mark.parametrize("counts", [[1, 5, 1, 2], [1, 701, 2, 1, 398]])
+def test_rows_blended_with_the_token_before(K, dtype, dim, pending, counts):
+    """Rows of 1, 5, 1 and 2 tokens in slots 3, 0, 2, 5 (and rows of hundreds of tokens, where a thread walks several
+    tokens and rows begin in the middle of its walk): a row's first token reads what its slot carries, later tokens
     the row before theirs (with what is pending added), and the slot receives the row's last normed row; a second step
     then reads it. Written out in 64-bit."""
-    counts, slots = [1, 5, 1, 2], [3, 0, 2, 5]
+    slots = [3, 0, 2, 5, 1][:len(counts)]
     rows, t = rows_of(counts, slots), sum(counts)
     post, pre, mix = triple(dim, 1), triple(dim, 3), torch.rand(dim, generator=torch.Generator().manual_seed(5))
     carried = rand(7, dim, seed=9)
